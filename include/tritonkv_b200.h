@@ -1,0 +1,126 @@
+/*
+ * tritonkv_b200 -- C ABI of the B200 (sm_100a) packed-KV decode-attention path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (cudaStream_t passed as void*), enqueues work on that stream, never
+ * synchronises, never allocates device memory and returns an int status
+ * (TKV_OK == 0).  After a non-zero status, tkv_last_error() returns a
+ * thread-local, human-readable description.
+ *
+ * Each declaration cites the interface of the reference project (PS12007/tritonkv)
+ * that it replaces, by file:line inside that project.
+ *
+ * Tensor layouts are the reference's, contiguous and row-major:
+ *   q        (B, HQ, D)                 f16 | bf16 | f32   (rounded to f16 in-kernel)
+ *   packed   (B, HKV, S, D*nbits/8)     uint8, split-P: byte j holds dims j, j+DP, ...
+ *                                       in ascending nbits-wide bit slices (DP = D*nbits/8)
+ *   scale,zero (B, HKV, S, D/gs)        f16, value = code*scale + zero
+ *   k, v     (B, HKV, S, D)             f16 (fp16 control path)
+ *   out      (B, HQ, D)                 f32
+ *   acc      (B, HQ, NS, D) f32, m and l (B, HQ, NS) f32: per-split partials,
+ *            acc = sum_n 2^(s_n-m) v_n, m = max_n s_n, l = sum_n 2^(s_n-m),
+ *            s_n = (q.k_n)*sm_scale*log2(e)   (the exp2 domain of the reference)
+ */
+#ifndef TRITONKV_B200_H_
+#define TRITONKV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TKV_OK 0
+#define TKV_ERR_INVALID 1     /* bad argument (shape, size, null pointer)            */
+#define TKV_ERR_UNSUPPORTED 2 /* valid in the reference, not built here (see text)   */
+#define TKV_ERR_CUDA 3        /* a CUDA runtime call failed                          */
+#define TKV_ERR_ALIGN 4       /* a base pointer is not 16-byte aligned               */
+
+#define TKV_DTYPE_F16 0
+#define TKV_DTYPE_BF16 1
+#define TKV_DTYPE_F32 2
+
+/* flags for the two decode entry points */
+#define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when num_splits == 1 */
+
+/* kernel ids for tkv_kernel_attrs */
+#define TKV_KERNEL_FUSED_SPLIT 0
+#define TKV_KERNEL_FP16_SPLIT 1
+#define TKV_KERNEL_COMBINE 2
+#define TKV_KERNEL_QUANTIZE_PACK 3
+
+/* Library version: major*10000 + minor*100 + patch. */
+int tkv_version(void);
+
+/* Thread-local description of the last failure of any call on this thread. */
+const char* tkv_last_error(void);
+
+/* SM count, L2 size and compute capability of `device`; what the reference reads
+ * from torch.cuda.get_device_properties (kernels/fused_decode_attn.py:410-413,
+ * benchmark.py replicas_for :625-638). */
+int tkv_device_info(int device, int* sm_count, int* l2_bytes, int* cc_major, int* cc_minor);
+
+/* Registers / static+dynamic shared memory / local memory / resident CTAs per SM of
+ * the instantiation that (nbits, D, gs) selects; replaces the Triton-cache
+ * introspection of probe_gs128.py:52-77 (n_regs, n_spills, metadata.shared). */
+int tkv_kernel_attrs(int kernel_id, int nbits, int D, int gs, int* regs, int* smem_bytes,
+                     int* local_bytes, int* ctas_per_sm);
+
+/* pack_codes (quantize.py:149-169): codes (rows, D) uint8 -> packed (rows, D*nbits/8). */
+int tkv_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t rows, int D, int nbits,
+                   void* stream);
+
+/* unpack_codes (quantize.py:172-183): the inverse. */
+int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t rows, int D, int nbits,
+                     void* stream);
+
+/* quantize_groupwise (quantize.py:186-236), one launch: per-group fp32 min/max,
+ * scale=(max-min)/qmax (1 if <= 0), scale and zero rounded to f16 first, then
+ * code = clamp(rint((x-zero)/scale), 0, qmax), packed split-P.  Bit-exact.
+ * x is (rows, D) of `in_dtype`. */
+int tkv_quantize_pack(const void* x, int in_dtype, uint8_t* packed, void* scale, void* zero,
+                      int64_t rows, int D, int nbits, int gs, void* stream);
+
+/* dequantize_groupwise (quantize.py:239-246): out (rows, D) of `out_dtype`,
+ * code*scale+zero evaluated in f32 then cast. */
+int tkv_dequantize(const uint8_t* packed, const void* scale, const void* zero, void* out,
+                   int out_dtype, int64_t rows, int D, int nbits, int gs, void* stream);
+
+/* _fused_decode_attn_split + launcher geometry (kernels/fused_decode_attn.py:155-353,
+ * :493-556).  One CTA per (batch, KV head, history split) serves the whole GQA group.
+ * Split s covers tokens [s*split_size, min((s+1)*split_size, S_b)); split_size must be
+ * a multiple of 16.  With num_splits == 1 and no TKV_FLAG_PARTIALS_ONLY the normalised
+ * result goes to `out` and acc/m/l may be null; otherwise partials go to acc/m/l and
+ * `out` is untouched (call tkv_combine next).  seq_lens (B,) int32 device pointer or
+ * null: per-sequence history length S_b <= S (no reference counterpart; null == S). */
+int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_packed, const void* k_scale,
+                     const void* k_zero, const uint8_t* v_packed, const void* v_scale,
+                     const void* v_zero, float* acc, float* m, float* l, float* out, int B,
+                     int HQ, int HKV, int S, int D, int nbits, int gs, float sm_scale,
+                     int num_splits, int split_size, const int32_t* seq_lens, int flags,
+                     void* stream);
+
+/* _fp16_decode_attn_split + launcher (kernels/fp16_decode_attn.py:47-135, :166-227):
+ * the control with the identical split, online softmax, GQA grouping and partial
+ * format, K/V read as plain f16. */
+int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const void* v, float* acc,
+                    float* m, float* l, float* out, int B, int HQ, int HKV, int S, int D,
+                    float sm_scale, int num_splits, int split_size, const int32_t* seq_lens,
+                    int flags, void* stream);
+
+/* _combine_splits (kernels/fused_decode_attn.py:355-395): log-sum-exp merge over NS
+ * partials.  out (B, HQ, D).  If out_m and out_l are non-null the merged result is
+ * left unnormalised in `out` with its (m, l) written there -- the wire format of a
+ * cross-GPU history split; otherwise out = acc / l. */
+int tkv_combine(const float* acc, const float* m, const float* l, float* out, float* out_m,
+                float* out_l, int B, int HQ, int NS, int D, void* stream);
+
+/* Resident CTAs per SM x SM count for the selected split kernel: the number of
+ * programs that fill the device in one wave; the launcher's target where the
+ * reference uses 4 x SM count (kernels/fused_decode_attn.py:402-416). */
+int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* programs);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITONKV_B200_H_ */

@@ -1,0 +1,343 @@
+"""GPU parity of the decode kernels against the CPU oracle (dequantise in fp32, then
+fp32 attention), through the C ABI.  The cases are the reference's kernel tests
+(test_correctness.py:141-343) plus its audit checks (audit_claims.py:1905-2015),
+with the elementwise bound |got-ref| <= 2e-3 + 1e-2*|ref| asserted next to the
+reference's own cosine / rel-L2 thresholds."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tkv_oracle as O
+from tritonkv_b200 import quantize as Q
+from tritonkv_b200.kernels import (combine_splits, fp16_decode_attention, fused_decode_attention,
+                                   triton_available)
+from tritonkv_b200.workloads import make_random_kv, ragged_seq_lens
+
+from util import ATOL, RTOL, assert_close, oracle_attention, to_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+SHAPES = [
+    (1, 12, 2, 128),  # Qwen2.5-1.5B attention shape
+    (1, 8, 8, 64),    # no GQA sharing (MHA)
+    (2, 32, 8, 64),   # Llama-3.2-1B shape, batch 2
+]
+SEQ_LENS = [1, 17, 128, 512, 2048, 8192, 16384]
+
+
+def _case(B, HQ, HKV, D, S, nbits, gs, seed, **kw):
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=seed)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    got = fused_decode_attention(q, kq, vq, **kw)
+    return got, oracle_attention(q, kq, vq), (q, k, v, kq, vq)
+
+
+def test_backend_reports_available():
+    ok, why = triton_available()
+    assert ok, why
+
+
+@pytest.mark.parametrize("S", SEQ_LENS)
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_kernel_matches_dequant_reference_4bit(S, seed):
+    got, ref, _ = _case(1, 12, 2, 128, S, 4, 32, seed)
+    assert_close(got, ref, f"S={S} seed={seed}")
+
+
+@pytest.mark.parametrize("S", [512, 2048, 8192, 16384])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_kernel_matches_dequant_reference_2bit(S, seed):
+    got, ref, _ = _case(1, 12, 2, 128, S, 2, 32, seed)
+    assert_close(got, ref, f"S={S} seed={seed}")
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("nbits", Q.SUPPORTED_BITS)
+def test_kernel_shapes_and_gqa(shape, nbits):
+    B, HQ, HKV, D = shape
+    got, ref, _ = _case(B, HQ, HKV, D, 1024, nbits, 32, seed=3)
+    assert_close(got, ref, f"{shape} {nbits}b")
+
+
+@pytest.mark.parametrize("D,gs", [(128, 16), (128, 32), (128, 64), (128, 128), (64, 16), (64, 32),
+                                  (64, 64)])
+@pytest.mark.parametrize("nbits", Q.SUPPORTED_BITS)
+def test_kernel_group_sizes(D, gs, nbits):
+    got, ref, _ = _case(1, 12, 2, D, 2048, nbits, gs, seed=4)
+    assert_close(got, ref, f"D={D} gs={gs} {nbits}b")
+
+
+@pytest.mark.parametrize("HQ,HKV", [(8, 1), (32, 8), (64, 8), (4, 4), (24, 2), (9, 3)])
+def test_gqa_group_sizes(HQ, HKV):
+    """Groups of 1..12 query heads per KV head (12 spans two head chunks of a CTA)."""
+    got, ref, _ = _case(2, HQ, HKV, 128, 777, 4, 32, seed=14)
+    assert_close(got, ref, f"HQ/HKV={HQ}/{HKV}")
+
+
+@pytest.mark.parametrize("num_splits", [1, 2, 5, 17, 64])
+def test_split_count_does_not_change_the_answer(num_splits):
+    got, ref, _ = _case(1, 12, 2, 128, 4096, 4, 32, seed=6, num_splits=num_splits)
+    assert_close(got, ref, f"splits={num_splits}")
+
+
+def test_split_counts_agree_with_each_other():
+    """audit_claims.py:1962-1985: spread across split counts below 2% of mean |out|."""
+    q, k, v = make_random_kv(1, 12, 2, 4096, 128, device=DEV, seed=21)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    outs = [fused_decode_attention(q, kq, vq, num_splits=n) for n in (1, 3, 8, 32)]
+    stack = torch.stack(outs)
+    spread = (stack.max(0).values - stack.min(0).values).max().item()
+    assert spread < 0.02 * stack[0].abs().mean().item()
+
+
+@pytest.mark.parametrize("block_n", [16, 32, 64, 128])
+def test_block_sizes(block_n):
+    got, ref, _ = _case(1, 12, 2, 128, 3000, 4, 32, seed=7, block_n=block_n)
+    assert_close(got, ref, f"BLOCK_N={block_n}")
+
+
+def test_output_is_finite_with_extreme_scores():
+    q, k, v = make_random_kv(1, 12, 2, 2048, 128, device=DEV, seed=8)
+    q = q * 50.0
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    got = fused_decode_attention(q, kq, vq)
+    assert torch.isfinite(got).all()
+    rep = O.allclose_report(got.cpu().numpy(), oracle_attention(q, kq, vq))
+    assert rep["cosine"] >= 0.99999 and rep["rel_l2"] <= 5e-3, rep
+
+
+def test_single_token_cache():
+    q, k, v = make_random_kv(1, 12, 2, 1, 128, device=DEV, seed=9)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    got = fused_decode_attention(q, kq, vq)
+    v_deq = Q.dequantize_groupwise(vq, torch.float32)
+    expect = v_deq[:, :, 0, :].repeat_interleave(6, dim=1)
+    assert ((got - expect).norm() / expect.norm()).item() < 1e-3
+
+
+def test_per_element_worst_case_not_hidden_by_aggregate():
+    got, ref, _ = _case(1, 12, 2, 128, 8192, 4, 32, seed=10)
+    err = np.abs(got.cpu().numpy() - ref)
+    assert err.max() / max(np.abs(ref).mean(), 1e-6) < 0.05
+
+
+def test_kernel_is_not_the_source_of_error():
+    """Kernel error vs the unquantised cache no worse than 1.5x the error of
+    dequantise-then-attend itself (test_correctness.py:202-217)."""
+    for S in (512, 2048, 8192):
+        got, ref_deq, (q, k, v, kq, vq) = _case(1, 12, 2, 128, S, 4, 32, seed=5)
+        truth = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
+                                             v.float().cpu().numpy())
+        e_kernel = O.allclose_report(got.cpu().numpy(), truth)["rel_l2"]
+        e_base = O.allclose_report(ref_deq, truth)["rel_l2"]
+        assert e_kernel <= 1.5 * e_base, (S, e_kernel, e_base)
+
+
+@pytest.mark.parametrize("S", [1, 17, 512, 2048])
+@pytest.mark.parametrize("nbits", Q.SUPPORTED_BITS)
+@pytest.mark.parametrize("gs", [16, 32, 64, 128])
+def test_variant_flags_are_bitwise_identical(S, nbits, gs):
+    """meta_bcast and dequant_fp16 must not change a single bit
+    (test_correctness.py:292-343); fold_zp stays within tolerance."""
+    q, k, v = make_random_kv(1, 12, 2, S, 128, device=DEV, seed=11)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    base = fused_decode_attention(q, kq, vq)
+    assert torch.equal(base, fused_decode_attention(q, kq, vq, meta_bcast=False))
+    assert torch.equal(base, fused_decode_attention(q, kq, vq, dequant_fp16=True))
+    assert torch.equal(base, fused_decode_attention(q, kq, vq, num_warps=8, num_stages=3))
+    assert_close(fused_decode_attention(q, kq, vq, fold_zp=True), oracle_attention(q, kq, vq))
+
+
+def test_heavy_outliers_and_peaked_softmax():
+    """audit_claims.py:1905-2015: 5% of entries x20, and a query aligned with one key."""
+    q, k, v = make_random_kv(1, 12, 2, 4096, 128, device=DEV, seed=31, outlier_frac=0.05,
+                             outlier_scale=20.0)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    rep = O.allclose_report(fused_decode_attention(q, kq, vq).cpu().numpy(),
+                            oracle_attention(q, kq, vq))
+    assert rep["cosine"] >= 0.99999 and rep["rel_l2"] <= 5e-3, rep
+    q2, k2, v2 = make_random_kv(1, 12, 2, 4096, 128, device=DEV, seed=32)
+    q2[0, :, :] = k2[0, 0, 1234, :] * 3.0
+    kq2, vq2 = Q.quantize_kv(k2, v2, 4, 32)
+    rep = O.allclose_report(fused_decode_attention(q2, kq2, vq2).cpu().numpy(),
+                            oracle_attention(q2, kq2, vq2))
+    assert rep["rel_l2"] <= 5e-3, rep
+
+
+@pytest.mark.parametrize("name", ["cfg1", "qwen_s17_2b", "mha_d64", "llama_b2_d64_g64",
+                                  "gqa8_g128_2b", "gqa4_g16"])
+def test_golden_attention_fixtures(golden_dir, name):
+    """Inputs and outputs stored from the reference's own quantize.py/reference.py."""
+    g = np.load(os.path.join(golden_dir, "attention.npz"))
+    B, HQ, HKV, S, D, nbits, gs, seed = [int(x) for x in g[f"{name}_meta"]]
+    def qt(t):
+        return Q.QuantizedTensor(torch.from_numpy(g[f"{name}_{t}packed"]).to(DEV),
+                                 torch.from_numpy(g[f"{name}_{t}scale"]).to(DEV),
+                                 torch.from_numpy(g[f"{name}_{t}zero"]).to(DEV), nbits, gs, D)
+    q = torch.from_numpy(g[f"{name}_q"]).to(DEV)
+    got = fused_decode_attention(q, qt("k"), qt("v"))
+    assert_close(got, g[f"{name}_out"], name)
+
+
+@pytest.mark.parametrize("q_dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_query_dtypes(q_dtype):
+    q, k, v = make_random_kv(1, 12, 2, 1000, 128, device=DEV, seed=40)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    qq = q.to(q_dtype)
+    got = fused_decode_attention(qq, kq, vq)
+    # the kernel rounds q to fp16, as the reference does; compare on that value
+    assert_close(got, oracle_attention(qq.to(torch.float16), kq, vq), str(q_dtype))
+
+
+def test_sm_scale_out_and_workspace_reuse():
+    q, k, v = make_random_kv(2, 8, 2, 2048, 128, device=DEV, seed=41)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    out = torch.empty(2, 8, 128, device=DEV)
+    ws = {}
+    r = fused_decode_attention(q, kq, vq, sm_scale=0.05, out=out, _workspace=ws, num_splits=8)
+    assert r is out and ws["key"] == (2, 8, 8, 128) and ws["acc"].shape == (2, 8, 8, 128)
+    acc_ptr = ws["acc"].data_ptr()
+    assert_close(out, oracle_attention(q, kq, vq, sm_scale=0.05))
+    fused_decode_attention(q, kq, vq, sm_scale=0.05, out=out, _workspace=ws, num_splits=8)
+    assert ws["acc"].data_ptr() == acc_ptr  # no reallocation
+    # the call is capturable and replayable once out and workspace exist
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fused_decode_attention(q, kq, vq, sm_scale=0.05, out=out, _workspace=ws, num_splits=8)
+    torch.cuda.current_stream().wait_stream(s)
+    with torch.cuda.graph(g):
+        fused_decode_attention(q, kq, vq, sm_scale=0.05, out=out, _workspace=ws, num_splits=8)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert_close(out, oracle_attention(q, kq, vq, sm_scale=0.05))
+
+
+def test_argument_errors_match_reference():
+    q, k, v = make_random_kv(1, 12, 2, 64, 128, device=DEV, seed=42)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    kq2, _ = Q.quantize_kv(k, v, 2, 32)
+    with pytest.raises(ValueError, match="same nbits/group_size"):
+        fused_decode_attention(q, kq2, vq)
+    with pytest.raises(ValueError, match="incompatible with cache"):
+        fused_decode_attention(q[:, :, :64].contiguous(), kq, vq)
+    with pytest.raises(ValueError, match="multiple of HKV"):
+        fused_decode_attention(q[:, :11].contiguous(), kq, vq)
+    kq8 = Q.quantize_groupwise(k, 4, 8)
+    with pytest.raises(ValueError, match="fold_zp needs group_size >= 16"):
+        fused_decode_attention(q, kq8, kq8, fold_zp=True)
+    with pytest.raises(ValueError, match="unsupported"):
+        fused_decode_attention(q, kq8, kq8)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fused_decode_attention(q.cpu(), kq, vq)
+
+
+# ------------------------------------------------------------------ fp16 control
+
+
+@pytest.mark.parametrize("S", [1, 17, 128, 2048, 16384])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fp16_control_matches_reference(S, shape):
+    B, HQ, HKV, D = shape
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=50)
+    got = fp16_decode_attention(q, k, v)
+    ref = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
+                                       v.float().cpu().numpy())
+    assert_close(got, ref, f"fp16 S={S} {shape}")
+
+
+@pytest.mark.parametrize("num_splits", [1, 3, 17])
+def test_fp16_control_splits(num_splits):
+    q, k, v = make_random_kv(1, 12, 2, 3000, 128, device=DEV, seed=51)
+    got = fp16_decode_attention(q, k, v, num_splits=num_splits, block_n=32)
+    ref = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
+                                       v.float().cpu().numpy())
+    assert_close(got, ref, f"fp16 splits={num_splits}")
+
+
+# ------------------------------------------------------------------ combine
+
+
+@pytest.mark.parametrize("NS", [1, 2, 7, 33, 300])
+@pytest.mark.parametrize("D", [64, 128])
+def test_combine_matches_oracle(NS, D):
+    g = torch.Generator().manual_seed(NS * 10 + D)
+    acc = torch.randn(2, 5, NS, D, generator=g)
+    m = torch.randn(2, 5, NS, generator=g) * 8
+    l = torch.rand(2, 5, NS, generator=g) * 50 + 0.1
+    if NS > 2:  # empty splits contribute nothing
+        m[:, :, 1] = float("-inf")
+        l[:, :, 1] = 0
+        acc[:, :, 1] = 0
+    ref = O.combine_splits(acc.numpy(), m.numpy(), l.numpy())
+    got = combine_splits(acc.to(DEV), m.to(DEV), l.to(DEV))
+    assert np.allclose(got.cpu().numpy(), ref, rtol=2e-5, atol=2e-6)
+    om = torch.empty(2, 5, device=DEV)
+    ol = torch.empty(2, 5, device=DEV)
+    raw = combine_splits(acc.to(DEV), m.to(DEV), l.to(DEV), out_m=om, out_l=ol)
+    assert np.allclose((raw / ol[..., None]).cpu().numpy(), ref, rtol=2e-5, atol=2e-6)
+    assert torch.equal(om.cpu(), m.max(dim=-1).values)
+
+
+def test_partials_match_oracle_format():
+    """(acc, m, l) of the split kernel in the exp2 domain against the oracle's
+    restatement of the reference's partial format."""
+    q, k, v = make_random_kv(1, 12, 2, 1024, 128, device=DEV, seed=60)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    ws = {}
+    fused_decode_attention(q, kq, vq, num_splits=4, block_n=64, _workspace=ws)
+    B, HQ, NS, D = ws["key"]
+    kd = O.dequantize_groupwise(to_oracle(kq))
+    vd = O.dequantize_groupwise(to_oracle(vq))
+    acc, m, l = O.split_partials(q.float().cpu().numpy(), kd, vd, 256, 4)
+    assert np.allclose(ws["maxs"].cpu().numpy(), m, atol=2e-3)
+    # compare partials on a common maximum (each warp-merged max may differ in the last ulps)
+    got = ws["acc"].cpu().numpy() * np.exp2(ws["maxs"].cpu().numpy() - m)[..., None]
+    assert np.linalg.norm(got - acc) / np.linalg.norm(acc) < 5e-3
+    assert np.allclose(ws["sums"].cpu().numpy() * np.exp2(ws["maxs"].cpu().numpy() - m), l, rtol=5e-3)
+
+
+# ------------------------------------------------------------------ ragged batches
+
+
+@pytest.mark.parametrize("nbits,D,gs,HQ,HKV", [(4, 128, 32, 32, 8), (2, 64, 64, 8, 1),
+                                               (4, 64, 32, 8, 1), (2, 128, 128, 32, 8)])
+def test_ragged_seq_lens(nbits, D, gs, HQ, HKV):
+    B, S = 6, 2500
+    lens = ragged_seq_lens(B, 1, S, seed=7)
+    lens[0] = S
+    lens[1] = 1
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=70)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    sl = lens.to(DEV)
+    got = fused_decode_attention(q, kq, vq, seq_lens=sl)
+    assert_close(got, oracle_attention(q, kq, vq, seq_lens=lens), "ragged fused")
+    got16 = fp16_decode_attention(q, k, v, seq_lens=sl)
+    ref16 = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
+                                         v.float().cpu().numpy(), seq_lens=lens.numpy())
+    assert_close(got16, ref16, "ragged fp16")
+
+
+def test_full_size_properties_llama8b_batch():
+    """Llama-3-8B shape, batch 8 of ctx 4096, at full per-sequence size: output is
+    a convex combination of dequantised V rows (bounded by their min/max per dim),
+    invariant to the split count, and equal to the oracle on one sampled sequence."""
+    B, HQ, HKV, S, D = 8, 32, 8, 4096, 128
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=80, outlier_frac=0.0)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    out = fused_decode_attention(q, kq, vq)
+    vd = Q.dequantize_groupwise(vq, torch.float32)
+    lo = vd.amin(dim=2).repeat_interleave(HQ // HKV, dim=1)
+    hi = vd.amax(dim=2).repeat_interleave(HQ // HKV, dim=1)
+    assert torch.all(out >= lo - 1e-3) and torch.all(out <= hi + 1e-3)
+    out2 = fused_decode_attention(q, kq, vq, num_splits=7)
+    assert (out - out2).abs().max().item() < 2e-3
+    b = 5
+    sub = lambda t: Q.QuantizedTensor(t.packed[b:b + 1], t.scale[b:b + 1], t.zero[b:b + 1], 4, 32, D)
+    assert_close(out[b:b + 1], oracle_attention(q[b:b + 1], sub(kq), sub(vq)), "sampled sequence")

@@ -1,0 +1,32 @@
+"""Helpers shared by the GPU parity tests: torch <-> numpy glue for the oracle."""
+
+import numpy as np
+import torch
+
+from oracle import tkv_oracle as O
+
+# Fused/fp16 kernel vs fp32 dequantise-then-attend on identical values
+# (test_correctness.py:51-52 of the reference) ...
+KERNEL_COSINE_MIN = 0.99999
+KERNEL_REL_L2_MAX = 5e-3
+# ... and the elementwise bound the target states: |got-ref| <= 2e-3 + 1e-2*|ref|.
+ATOL, RTOL = 2e-3, 1e-2
+
+
+def to_oracle(qt) -> O.OracleQuantized:
+    return O.OracleQuantized(qt.packed.cpu().numpy(), qt.scale.cpu().numpy(), qt.zero.cpu().numpy(),
+                             qt.nbits, qt.group_size, qt.head_dim)
+
+
+def oracle_attention(q, kq, vq, sm_scale=None, seq_lens=None) -> np.ndarray:
+    sl = None if seq_lens is None else seq_lens.cpu().numpy()
+    return O.reference_on_quantized(q.float().cpu().numpy(), to_oracle(kq), to_oracle(vq),
+                                    sm_scale, sl)
+
+
+def assert_close(got: torch.Tensor, ref: np.ndarray, what=""):
+    rep = O.allclose_report(got.float().cpu().numpy(), ref, ATOL, RTOL)
+    assert rep["ok"], f"{what}: {rep}"
+    assert rep["cosine"] >= KERNEL_COSINE_MIN, f"{what}: {rep}"
+    assert rep["rel_l2"] <= KERNEL_REL_L2_MAX, f"{what}: {rep}"
+    return rep

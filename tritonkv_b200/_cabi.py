@@ -1,0 +1,157 @@
+"""ctypes binding of ``libtritonkv_b200.so`` (the C ABI declared in
+``include/tritonkv_b200.h``).
+
+The library is the only compute path of this package.  If it is missing or does
+not load, every operation raises ``RuntimeError``: there is no fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtritonkv_b200.so")
+
+TKV_OK = 0
+TKV_ERR_INVALID = 1
+TKV_ERR_UNSUPPORTED = 2
+TKV_ERR_CUDA = 3
+TKV_ERR_ALIGN = 4
+
+DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
+FLAG_PARTIALS_ONLY = 1
+KERNEL_FUSED_SPLIT, KERNEL_FP16_SPLIT = 0, 1
+
+_TORCH_DTYPE = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32}
+
+# Every symbol include/tritonkv_b200.h declares: (restype, argtypes).
+SIGNATURES = {
+    "tkv_version": (c_int, []),
+    "tkv_last_error": (c_char_p, []),
+    "tkv_device_info": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "tkv_kernel_attrs": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
+                                 POINTER(c_int), POINTER(c_int)]),
+    "tkv_pack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "tkv_unpack_codes": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "tkv_quantize_pack": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                  c_int, c_int, c_void_p]),
+    "tkv_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+                               c_int, c_void_p]),
+    "tkv_fused_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                 c_int, c_void_p]),
+    "tkv_fp16_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                c_void_p, c_int, c_void_p]),
+    "tkv_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_int, c_void_p]),
+    "tkv_wave_programs": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
+}
+
+_lib = None
+_load_error: Exception | None = None
+
+
+def load():
+    """Return the loaded library, or raise ``RuntimeError`` (never falls back)."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if _load_error is None:
+        try:
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+            return _lib
+        except Exception as exc:  # missing file, missing symbol, loader error
+            _load_error = exc
+    raise RuntimeError(
+        f"tritonkv_b200: CUDA library {LIB_PATH} is not available ({_load_error!r}); "
+        "build it with `python -m tritonkv_b200.build`. There is no CPU or PyTorch fallback."
+    )
+
+
+def available() -> tuple[bool, str]:
+    """(usable, why): the library loads and a CUDA device is present."""
+    try:
+        lib = load()
+    except RuntimeError as exc:
+        return False, str(exc)
+    if not torch.cuda.is_available():
+        return False, "torch.cuda.is_available() is False"
+    return True, f"tritonkv_b200 {lib.tkv_version()} (CUDA sm_100a, C ABI)"
+
+
+def last_error() -> str:
+    return load().tkv_last_error().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    """Map a C-ABI status to the exception type the reference raises."""
+    if status == TKV_OK:
+        return
+    msg = last_error()
+    if status in (TKV_ERR_INVALID, TKV_ERR_UNSUPPORTED, TKV_ERR_ALIGN):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _TORCH_DTYPE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float16, bfloat16 or float32") from None
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"tritonkv_b200: {what} must be a CUDA tensor (got device {t.device}); "
+            "this package has no CPU path"
+        )
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def device_info(device: int | None = None) -> dict:
+    lib = load()
+    if device is None:
+        device = torch.cuda.current_device()
+    vals = [c_int(0) for _ in range(4)]
+    check(lib.tkv_device_info(device, *[ctypes.byref(v) for v in vals]))
+    return {"sm_count": vals[0].value, "l2_bytes": vals[1].value,
+            "cc": (vals[2].value, vals[3].value)}
+
+
+def kernel_attrs(kernel_id: int, nbits: int, D: int, gs: int) -> dict:
+    lib = load()
+    vals = [c_int(0) for _ in range(4)]
+    check(lib.tkv_kernel_attrs(kernel_id, nbits, D, gs, *[ctypes.byref(v) for v in vals]))
+    return {"regs": vals[0].value, "smem_bytes": vals[1].value, "local_bytes": vals[2].value,
+            "ctas_per_sm": vals[3].value}
+
+
+_wave_cache: dict = {}
+
+
+def wave_programs(kernel_id: int, nbits: int, D: int, gs: int) -> int:
+    key = (kernel_id, nbits, D, gs, torch.cuda.current_device())
+    if key not in _wave_cache:
+        v = c_int(0)
+        check(load().tkv_wave_programs(kernel_id, nbits, D, gs, ctypes.byref(v)))
+        _wave_cache[key] = v.value
+    return _wave_cache[key]

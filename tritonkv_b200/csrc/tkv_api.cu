@@ -1,0 +1,71 @@
+// Library-level entry points: error text, device facts, kernel resource queries.
+#include <stdarg.h>
+
+#include "tkv_common.cuh"
+
+namespace tkv {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int* ctas);
+int fp16_attrs(int D, int* regs, int* smem, int* local, int* ctas);
+
+}  // namespace tkv
+
+using namespace tkv;
+
+extern "C" int tkv_version(void) { return 100; }
+
+extern "C" const char* tkv_last_error(void) { return g_error; }
+
+extern "C" int tkv_device_info(int device, int* sm_count, int* l2_bytes, int* cc_major,
+                               int* cc_minor) {
+  int v = 0;
+  if (sm_count) {
+    TKV_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+    *sm_count = v;
+  }
+  if (l2_bytes) {
+    TKV_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, device));
+    *l2_bytes = v;
+  }
+  if (cc_major) {
+    TKV_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, device));
+    *cc_major = v;
+  }
+  if (cc_minor) {
+    TKV_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMinor, device));
+    *cc_minor = v;
+  }
+  return TKV_OK;
+}
+
+extern "C" int tkv_kernel_attrs(int kernel_id, int nbits, int D, int gs, int* regs,
+                                int* smem_bytes, int* local_bytes, int* ctas_per_sm) {
+  switch (kernel_id) {
+    case TKV_KERNEL_FUSED_SPLIT:
+      return fused_attrs(nbits, D, gs, regs, smem_bytes, local_bytes, ctas_per_sm);
+    case TKV_KERNEL_FP16_SPLIT:
+      return fp16_attrs(D, regs, smem_bytes, local_bytes, ctas_per_sm);
+  }
+  set_error("kernel_attrs: kernel id %d has no per-instantiation attributes", kernel_id);
+  return TKV_ERR_INVALID;
+}
+
+extern "C" int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* programs) {
+  TKV_REQUIRE(programs, TKV_ERR_INVALID, "wave_programs: null output");
+  int ctas = 0, sms = 0, dev = 0;
+  int rc = tkv_kernel_attrs(kernel_id, nbits, D, gs, nullptr, nullptr, nullptr, &ctas);
+  if (rc != TKV_OK) return rc;
+  TKV_CUDA(cudaGetDevice(&dev));
+  TKV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  *programs = ctas * sms;
+  return TKV_OK;
+}
