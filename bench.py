@@ -59,6 +59,10 @@ def parse_args():
     ap.add_argument("--nbits", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--no-table", action="store_true", help="skip the sweep rows")
+    ap.add_argument("--batch", type=int, default=None, help="override the workload's batch size")
+    ap.add_argument("--light", action="store_true",
+                    help="timed region only: no sweep rows, CPU baseline, end-to-end leg or "
+                         "oracle check (for profiler captures)")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -228,6 +232,9 @@ def run_ours(args):
     B, HQ, HKV, D, ctx, nbits, desc = WORKLOADS[args.workload]
     ctx = args.ctx or ctx
     nbits = args.nbits or nbits
+    B = args.batch or B
+    if args.light:
+        args.no_table = True
     K, W = max(1, args.steps), max(3, args.warmup)
     info = _cabi.device_info(local)
     l2 = info["l2_bytes"]
@@ -251,7 +258,7 @@ def run_ours(args):
 
     # ---- parity of copy 0 against the CPU oracle (the checker, not the timed thing) ----
     parity = None
-    if rank == 0 and B * HKV * S_local <= 2 * 131072:
+    if rank == 0 and not args.light and B * HKV * S_local <= 2 * 131072:
         from oracle import tkv_oracle as O
         r0 = reps[0]
         got = fused_decode_attention(r0["q"], r0["kq"], r0["vq"]).cpu().numpy()
@@ -357,7 +364,7 @@ def run_ours(args):
             stream.synchronize()  # the host reads this step's result before the next one
 
     e2e = None
-    if not history_split:
+    if not history_split and not args.light:
         e2e_steps(min(50, K_e2e))
         ms_e2e = max_over_ranks(harness.time_region(lambda: e2e_steps(K_e2e), barrier))
         e2e = {"value": total_bytes * K_e2e / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
@@ -377,7 +384,7 @@ def run_ours(args):
 
     # ---- CPU baseline on this box's host cores (rank 0, single GPU only) ----
     cpu = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.light:
         r0 = reps[0]
         S_cpu = min(S_local, 8192)
         def host(t):

@@ -41,7 +41,7 @@ extern "C" {
 #define TKV_DTYPE_F32 2
 
 /* flags for the two decode entry points */
-#define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when num_splits == 1 */
+#define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when nslots == 1 */
 
 /* kernel ids for tkv_kernel_attrs */
 #define TKV_KERNEL_FUSED_SPLIT 0
@@ -86,27 +86,39 @@ int tkv_quantize_pack(const void* x, int in_dtype, uint8_t* packed, void* scale,
 int tkv_dequantize(const uint8_t* packed, const void* scale, const void* zero, void* out,
                    int out_dtype, int64_t rows, int D, int nbits, int gs, void* stream);
 
+/* Work plan of a decode call: how many partial slots per (batch, query head) the split
+ * kernel will write (`nslots`, the third dimension of acc/m/l) and how many CTAs it
+ * launches.  kernel_id is TKV_KERNEL_FUSED_SPLIT (nbits, D, gs select the instantiation)
+ * or TKV_KERNEL_FP16_SPLIT (nbits and gs ignored).  The split geometry is the
+ * reference's (kernels/fused_decode_attn.py:493-499): num_splits splits of split_size
+ * tokens (a multiple of 16), none empty; the kernels further cut the work into
+ * equal per-CTA tile ranges, so nslots >= num_splits.  ragged != 0 plans for a call
+ * that passes seq_lens. */
+int tkv_decode_plan(int kernel_id, int nbits, int D, int gs, int B, int HQ, int HKV, int S,
+                    int num_splits, int split_size, int ragged, int* nslots, int* grid);
+
 /* _fused_decode_attn_split + launcher geometry (kernels/fused_decode_attn.py:155-353,
- * :493-556).  One CTA per (batch, KV head, history split) serves the whole GQA group.
- * Split s covers tokens [s*split_size, min((s+1)*split_size, S_b)); split_size must be
- * a multiple of 16.  With num_splits == 1 and no TKV_FLAG_PARTIALS_ONLY the normalised
- * result goes to `out` and acc/m/l may be null; otherwise partials go to acc/m/l and
- * `out` is untouched (call tkv_combine next).  seq_lens (B,) int32 device pointer or
- * null: per-sequence history length S_b <= S (no reference counterpart; null == S). */
+ * :493-556).  One CTA segment per (batch, KV head, history split) serves the whole GQA
+ * group.  Split s covers tokens [s*split_size, min((s+1)*split_size, S_b)).  With
+ * nslots == 1 (from tkv_decode_plan) and no TKV_FLAG_PARTIALS_ONLY the normalised result
+ * goes to `out` and acc/m/l may be null; otherwise partials go to acc (B,HQ,nslots,D),
+ * m, l (B,HQ,nslots) and `out` is untouched (call tkv_combine with NS = nslots next).
+ * seq_lens (B,) int32 device pointer or null: per-sequence history length S_b <= S (no
+ * reference counterpart; null == S). */
 int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_packed, const void* k_scale,
                      const void* k_zero, const uint8_t* v_packed, const void* v_scale,
                      const void* v_zero, float* acc, float* m, float* l, float* out, int B,
                      int HQ, int HKV, int S, int D, int nbits, int gs, float sm_scale,
-                     int num_splits, int split_size, const int32_t* seq_lens, int flags,
-                     void* stream);
+                     int num_splits, int split_size, int nslots, const int32_t* seq_lens,
+                     int flags, void* stream);
 
 /* _fp16_decode_attn_split + launcher (kernels/fp16_decode_attn.py:47-135, :166-227):
- * the control with the identical split, online softmax, GQA grouping and partial
- * format, K/V read as plain f16. */
+ * the control with the identical split, scheduling, online softmax, GQA grouping and
+ * partial format, K/V read as plain f16. */
 int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const void* v, float* acc,
                     float* m, float* l, float* out, int B, int HQ, int HKV, int S, int D,
-                    float sm_scale, int num_splits, int split_size, const int32_t* seq_lens,
-                    int flags, void* stream);
+                    float sm_scale, int num_splits, int split_size, int nslots,
+                    const int32_t* seq_lens, int flags, void* stream);
 
 /* _combine_splits (kernels/fused_decode_attn.py:355-395): log-sum-exp merge over NS
  * partials.  out (B, HQ, D).  If out_m and out_l are non-null the merged result is
@@ -119,6 +131,12 @@ int tkv_combine(const float* acc, const float* m, const float* l, float* out, fl
  * programs that fill the device in one wave; the launcher's target where the
  * reference uses 4 x SM count (kernels/fused_decode_attn.py:402-416). */
 int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* programs);
+
+/* Device-side status word of the current device (synchronises with it): 0 = ok,
+ * 1 = a bounded wait on a copy barrier inside a decode kernel gave up (the kernel then
+ * returned early and its output is invalid).  No reference counterpart: the Triton
+ * kernels have no waits of their own. */
+int tkv_device_status(int* status);
 
 #ifdef __cplusplus
 }

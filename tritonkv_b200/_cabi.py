@@ -43,14 +43,17 @@ SIGNATURES = {
                                c_int, c_void_p]),
     "tkv_fused_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
-                                 c_int, c_void_p]),
+                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                 c_void_p, c_int, c_void_p]),
     "tkv_fp16_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                c_void_p, c_int, c_void_p]),
+                                c_int, c_void_p, c_int, c_void_p]),
     "tkv_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_void_p]),
     "tkv_wave_programs": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
+    "tkv_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, POINTER(c_int), POINTER(c_int)]),
+    "tkv_device_status": (c_int, [POINTER(c_int)]),
 }
 
 _lib = None
@@ -143,6 +146,32 @@ def kernel_attrs(kernel_id: int, nbits: int, D: int, gs: int) -> dict:
     check(lib.tkv_kernel_attrs(kernel_id, nbits, D, gs, *[ctypes.byref(v) for v in vals]))
     return {"regs": vals[0].value, "smem_bytes": vals[1].value, "local_bytes": vals[2].value,
             "ctas_per_sm": vals[3].value}
+
+
+def device_status() -> int:
+    """0 = ok; 1 = a bounded wait inside a decode kernel gave up (synchronises)."""
+    v = c_int(0)
+    check(load().tkv_device_status(ctypes.byref(v)))
+    return v.value
+
+
+_plan_cache: dict = {}
+
+
+def decode_plan(kernel_id: int, nbits: int, D: int, gs: int, B: int, HQ: int, HKV: int, S: int,
+                num_splits: int, split_size: int, ragged: bool) -> tuple[int, int]:
+    """(nslots, grid): partial slots per (batch, head) and CTAs of the split kernel."""
+    key = (kernel_id, nbits, D, gs, B, HQ, HKV, S, num_splits, split_size, ragged,
+           torch.cuda.current_device())
+    r = _plan_cache.get(key)
+    if r is None:
+        ns, grid = c_int(0), c_int(0)
+        check(load().tkv_decode_plan(kernel_id, nbits, D, gs, B, HQ, HKV, S, num_splits, split_size,
+                                     1 if ragged else 0, ctypes.byref(ns), ctypes.byref(grid)))
+        r = (ns.value, grid.value)
+        if len(_plan_cache) < 4096:
+            _plan_cache[key] = r
+    return r
 
 
 _wave_cache: dict = {}

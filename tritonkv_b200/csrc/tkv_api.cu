@@ -1,7 +1,7 @@
 // Library-level entry points: error text, device facts, kernel resource queries.
 #include <stdarg.h>
 
-#include "tkv_common.cuh"
+#include "tkv_splitk_driver.cuh"
 
 namespace tkv {
 
@@ -16,6 +16,12 @@ void set_error(const char* fmt, ...) {
 
 int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int* ctas);
 int fp16_attrs(int D, int* regs, int* smem, int* local, int* ctas);
+int fused_device_status(int* status);
+int fp16_device_status(int* status);
+int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
+               int num_splits, int split_size, bool ragged);
+int fp16_plan(int D, SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
+              int split_size, bool ragged);
 
 }  // namespace tkv
 
@@ -59,6 +65,32 @@ extern "C" int tkv_kernel_attrs(int kernel_id, int nbits, int D, int gs, int* re
   return TKV_ERR_INVALID;
 }
 
+extern "C" int tkv_decode_plan(int kernel_id, int nbits, int D, int gs, int B, int HQ, int HKV,
+                               int S, int num_splits, int split_size, int ragged, int* nslots,
+                               int* grid) {
+  TKV_REQUIRE(B > 0 && HQ > 0 && HKV > 0 && S > 0 && HQ % HKV == 0, TKV_ERR_INVALID,
+              "decode_plan: bad sizes B=%d HQ=%d HKV=%d S=%d", B, HQ, HKV, S);
+  TKV_REQUIRE(num_splits >= 1 && split_size >= 16 && split_size % 16 == 0 &&
+                  (int64_t)num_splits * split_size >= S && (int64_t)(num_splits - 1) * split_size < S,
+              TKV_ERR_INVALID, "decode_plan: %d splits of %d tokens must cover S=%d with no empty split",
+              num_splits, split_size, S);
+  const int hchunks = (HQ / HKV + kHeadsPerCta - 1) / kHeadsPerCta;
+  SplitSched sc;
+  int rc;
+  if (kernel_id == TKV_KERNEL_FUSED_SPLIT)
+    rc = fused_plan(nbits, D, gs, &sc, B, HKV, hchunks, S, num_splits, split_size, ragged != 0);
+  else if (kernel_id == TKV_KERNEL_FP16_SPLIT)
+    rc = fp16_plan(D, &sc, B, HKV, hchunks, S, num_splits, split_size, ragged != 0);
+  else {
+    set_error("decode_plan: kernel id %d is not a split kernel", kernel_id);
+    return TKV_ERR_INVALID;
+  }
+  if (rc != TKV_OK) return rc;
+  if (nslots) *nslots = sc.nslots;
+  if (grid) *grid = sc.grid;
+  return TKV_OK;
+}
+
 extern "C" int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* programs) {
   TKV_REQUIRE(programs, TKV_ERR_INVALID, "wave_programs: null output");
   int ctas = 0, sms = 0, dev = 0;
@@ -67,5 +99,16 @@ extern "C" int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* p
   TKV_CUDA(cudaGetDevice(&dev));
   TKV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   *programs = ctas * sms;
+  return TKV_OK;
+}
+
+extern "C" int tkv_device_status(int* status) {
+  TKV_REQUIRE(status, TKV_ERR_INVALID, "device_status: null output");
+  int a = 0, b = 0;
+  int rc = fused_device_status(&a);
+  if (rc != TKV_OK) return rc;
+  rc = fp16_device_status(&b);
+  if (rc != TKV_OK) return rc;
+  *status = a | b;
   return TKV_OK;
 }

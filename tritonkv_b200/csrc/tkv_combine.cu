@@ -2,65 +2,96 @@
 //
 // Replaces _combine_splits of the reference (kernels/fused_decode_attn.py:355-395):
 //     out = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),   M = max_s m_s
-// One warp per (batch, query head).  The global maximum is found first (lanes
-// stride over the splits, warp-shuffle max), then every lane accumulates its
-// float4 slice of D over the splits; splits with m = -inf (empty) weigh zero.
-// With out_m/out_l given, the merged partial is written unnormalised together
-// with (M, L): the wire format of a cross-GPU history split.
+// The reference walks the splits sequentially in one program per (batch, head); with
+// a device-filling split count (hundreds at batch 1) that loop is a chain of
+// dependent L2 round trips.  Here one CTA of 256 threads owns a (batch, head, 32-dim
+// slice): the maximum is a block reduction, then 32 thread groups each take every
+// 32nd split with independent float4 loads, and the groups are summed through warp
+// shuffles and shared memory.  Splits with m = -inf (empty) weigh zero.
+// With out_m/out_l given, the merged partial is written unnormalised together with
+// (M, L): the wire format of a cross-GPU history split.
 #include "tkv_common.cuh"
 
 namespace tkv {
 
-constexpr int kCombineWarps = 4;
+constexpr int kCombineThreads = 256;
+constexpr int kCombineSlice = 32;  // head dims per CTA
 
-__global__ void __launch_bounds__(kCombineWarps * 32)
+__global__ void __launch_bounds__(kCombineThreads)
     combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
                    const float* __restrict__ l, float* __restrict__ out, float* __restrict__ out_m,
-                   float* __restrict__ out_l, int rows, int NS, int D) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * kCombineWarps + warp;  // b*HQ + h
-  if (row >= rows) return;
+                   float* __restrict__ out_l, int NS, int D) {
+  __shared__ float red_m[8];
+  __shared__ float4 red_a[8][8];
+  __shared__ float red_l[8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = blockIdx.x;            // b*HQ + h
+  const int d0 = blockIdx.y * kCombineSlice;
+  const int sg = tid >> 3, dl = tid & 7; // split group (0..31), float4 index inside the slice
   const float* mrow = m + (int64_t)row * NS;
   const float* lrow = l + (int64_t)row * NS;
-  const float* arow = acc + (int64_t)row * NS * D;
+  const float* arow = acc + (int64_t)row * NS * D + d0 + dl * 4;
 
-  float M = -INFINITY;
-  for (int s = lane; s < NS; s += 32) M = fmaxf(M, mrow[s]);
+  float mloc = -INFINITY;
+  for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s));
 #pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(kFullMask, M, off));
+  for (int off = 16; off >= 1; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
+  if (lane == 0) red_m[warp] = mloc;
+  __syncthreads();
+  float M = red_m[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
 
-  const int nvec = D >> 2;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
   float L = 0.f;
-  for (int v0 = 0; v0 < nvec; v0 += 32) {
-    const int v = v0 + lane;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    float Lloc = 0.f;
-    if (v < nvec) {
 #pragma unroll 4
-      for (int s = 0; s < NS; ++s) {
-        const float ms = __ldg(mrow + s);
-        const float w = (ms == -INFINITY) ? 0.f : ex2(ms - M);
-        const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * D) + v);
-        a.x = fmaf(w, x.x, a.x);
-        a.y = fmaf(w, x.y, a.y);
-        a.z = fmaf(w, x.z, a.z);
-        a.w = fmaf(w, x.w, a.w);
-        Lloc = fmaf(w, __ldg(lrow + s), Lloc);
-      }
-      L = Lloc;
-      if (out_m == nullptr) {
-        const float inv = Lloc > 0.f ? 1.f / Lloc : 0.f;
-        a.x *= inv;
-        a.y *= inv;
-        a.z *= inv;
-        a.w *= inv;
-      }
-      reinterpret_cast<float4*>(out + (int64_t)row * D)[v] = a;
+  for (int s = sg; s < NS; s += 32) {
+    const float ms = __ldg(mrow + s);
+    if (ms > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never read it
+      const float w = ex2(ms - M);
+      const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * D));
+      a.x = fmaf(w, x.x, a.x);
+      a.y = fmaf(w, x.y, a.y);
+      a.z = fmaf(w, x.z, a.z);
+      a.w = fmaf(w, x.w, a.w);
+      L = fmaf(w, __ldg(lrow + s), L);
     }
   }
-  if (out_m != nullptr && lane == 0) {
-    out_m[row] = M;
-    out_l[row] = L;
+  // the 4 split groups of a warp (lanes dl, dl+8, dl+16, dl+24)
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+    a.x += __shfl_xor_sync(kFullMask, a.x, off);
+    a.y += __shfl_xor_sync(kFullMask, a.y, off);
+    a.z += __shfl_xor_sync(kFullMask, a.z, off);
+    a.w += __shfl_xor_sync(kFullMask, a.w, off);
+    L += __shfl_xor_sync(kFullMask, L, off);
+  }
+  if (lane < 8) red_a[warp][lane] = a;
+  if (lane == 0) red_l[warp] = L;
+  __syncthreads();
+  if (tid < 8) {
+    float4 r = red_a[0][tid];
+    float Lt = red_l[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      const float4 x = red_a[w][tid];
+      r.x += x.x;
+      r.y += x.y;
+      r.z += x.z;
+      r.w += x.w;
+      Lt += red_l[w];
+    }
+    if (out_m == nullptr) {
+      const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
+      r.x *= inv;
+      r.y *= inv;
+      r.z *= inv;
+      r.w *= inv;
+    } else if (tid == 0 && blockIdx.y == 0) {
+      out_m[row] = M;
+      out_l[row] = Lt;
+    }
+    *reinterpret_cast<float4*>(out + (int64_t)row * D + d0 + tid * 4) = r;
   }
 }
 
@@ -72,15 +103,15 @@ extern "C" int tkv_combine(const float* acc, const float* m, const float* l, flo
   TKV_REQUIRE(acc && m && l && out, TKV_ERR_INVALID, "combine: null pointer");
   TKV_REQUIRE((out_m == nullptr) == (out_l == nullptr), TKV_ERR_INVALID,
               "combine: out_m and out_l must be given together");
-  TKV_REQUIRE(B > 0 && HQ > 0 && NS > 0 && D > 0 && D % 4 == 0, TKV_ERR_INVALID,
-              "combine: bad sizes B=%d HQ=%d NS=%d D=%d", B, HQ, NS, D);
+  TKV_REQUIRE(B > 0 && HQ > 0 && NS > 0 && D > 0 && D % kCombineSlice == 0, TKV_ERR_INVALID,
+              "combine: bad sizes B=%d HQ=%d NS=%d D=%d (D must be a multiple of 32)", B, HQ, NS, D);
   TKV_REQUIRE(aligned16(acc) && aligned16(out), TKV_ERR_ALIGN,
               "combine: acc and out must be 16-byte aligned");
   const int64_t rows = (int64_t)B * HQ;
-  TKV_REQUIRE(rows <= (1LL << 30), TKV_ERR_INVALID, "combine: too many rows");
-  const int blocks = (int)((rows + kCombineWarps - 1) / kCombineWarps);
-  combine_kernel<<<blocks, kCombineWarps * 32, 0, (cudaStream_t)stream>>>(acc, m, l, out, out_m,
-                                                                        out_l, (int)rows, NS, D);
+  TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
+  dim3 grid((unsigned)rows, D / kCombineSlice);
+  combine_kernel<<<grid, kCombineThreads, 0, (cudaStream_t)stream>>>(acc, m, l, out, out_m, out_l,
+                                                                     NS, D);
   TKV_CUDA(cudaGetLastError());
   return TKV_OK;
 }

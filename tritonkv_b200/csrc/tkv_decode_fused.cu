@@ -2,11 +2,17 @@
 //
 // Replaces _fused_decode_attn_split of the reference (kernels/fused_decode_attn.py:155-353).
 //
-// One CTA serves one (batch, KV head, history split) and up to 8 query heads of the
-// GQA group.  Inside the CTA every warp is an independent stream: it owns a private
-// ring of shared-memory stages filled with 16-byte cp.async copies, walks its own
-// 16-token tiles of the split, and keeps a private online-softmax state; the warps'
-// results are merged once, in the epilogue.  No CTA-wide barrier sits in the loop.
+// Scheduling, the per-warp copy rings and the epilogue live in tkv_splitk_driver.cuh
+// (persistent CTAs over balanced tile ranges; one CTA segment serves one (batch, KV
+// head, history split) and up to 8 query heads of the GQA group).  This file is the
+// tile policy: how a 32-token tile is fetched and what is computed on it.
+//
+// Data movement.  A stage holds 32 tokens: K codes, V codes, and the four scale/zero
+// arrays.  Lane 0 of the warp fills it with two tiled TMA loads (tensor maps over the
+// packed code tensors viewed as [tokens, bytes-per-token], hardware 32B/64B swizzle so
+// that the later ldmatrix reads are bank-conflict free) and four 1-D bulk copies for
+// the metadata, all completing on one mbarrier per stage.  Ragged tails and caches
+// whose metadata rows are not 16-byte aligned fetch the metadata with plain loads.
 //
 // Arithmetic.  The packed bytes are never expanded to dequantised values.  With
 // code c, group scale s and group zero z, a cache value is c*s + z, so
@@ -16,22 +22,31 @@
 // A operand is the raw code field, isolated from the packed word by ONE bitwise AND:
 // a 2- or 4-bit field inside the mantissa of an f16 is the subnormal (or scaled)
 // number c * 2^(pos-24), exact, and the power of two is folded into the f32 scale
-// afterwards.  The zero-point terms are one extra MMA each per tile.  Per packed
-// 32-bit word (8 or 16 codes) the integer work is one shift and P*2 ANDs.
+// afterwards.  The zero-point terms are one extra MMA each per 16 tokens.
 //
-// Fragment mapping (g = lane/4, t = lane%4).  Scores use S^T = K Q^T with the 16
-// tokens of a tile as MMA rows and the 8 heads as columns; the output uses
-// O^T = V^T P^T with 16 head-dims as rows.  ldmatrix delivers for K the 4 bytes
-// [16b+4t, 16b+4t+4) of tokens g / g+8, and with .trans for V the 2 bytes
-// [16b+2g, 16b+2g+2) of token pairs (2t, 2t+1) / (2t+8, 2t+9) -- already in the
-// layout of an A fragment once masked.  Chunk ch = slice*NBLK + b covers head dims
-// [16ch, 16ch+16) because of the split-P layout (byte j, bit slice p -> dim j + p*DP).
-#include "tkv_split_common.cuh"
+// Fragment mapping (g = lane/4, t = lane%4).  Scores use S^T = K Q^T with 16 tokens
+// as MMA rows and the 8 heads as columns; the output uses O^T = V^T P^T with 16
+// head-dims as rows.  ldmatrix delivers for K the 4 bytes [16b+4t, 16b+4t+4) of
+// tokens g / g+8, and with .trans for V the 2 bytes [16b+2g, 16b+2g+2) of token
+// pairs (2t, 2t+1) / (2t+8, 2t+9) -- already the layout of an A fragment once masked.
+// Chunk ch = slice*NBLK + b covers head dims [16ch, 16ch+16) because of the split-P
+// layout (byte j, bit slice p -> dim j + p*DP).
+//
+// Softmax.  Probabilities are taken relative to a reference exponent m_ref that is
+// only raised (to tile max + 4) when a tile exceeds it, so accumulators are rescaled
+// a handful of times per split instead of at almost every tile; the true running
+// maximum is tracked separately and the partial is converted to it in the epilogue.
+#include <cuda.h>
+
+#include "tkv_splitk_driver.cuh"
 
 namespace tkv {
 
+constexpr int kTok = 32;  // tokens per tile / stage
+
 template <int NBITS, int D, int GS>
 struct FusedCfg {
+  static constexpr int NBITS_ = NBITS, D_ = D, GS_ = GS;
   static constexpr int P = 8 / NBITS;          // codes per byte = bit slices
   static constexpr int DP = D / P;             // packed bytes per token
   static constexpr int NBLK = DP / 16;         // 16-byte column blocks per token row
@@ -39,177 +54,222 @@ struct FusedCfg {
   static constexpr int NG = D / GS;            // quantisation groups per token
   static constexpr int ACC_DIMS = (GS < DP) ? GS : DP;  // dims sharing one score accumulator
   static constexpr int NACC = D / ACC_DIMS;
-  static constexpr int CODE_BYTES = kTile * DP;
-  static constexpr int META_BYTES = kTile * NG * 2;
-  static constexpr int STAGE_BYTES = 2 * CODE_BYTES + 4 * META_BYTES;
+  static constexpr int CODE_BYTES = (kTok * DP + 1023) / 1024 * 1024;  // keeps V's swizzle phase
+  static constexpr int NPAIR = (NBLK + 1) / 2;  // ldmatrix issues per 16-token half
+  static constexpr int META_BYTES = kTok * NG * 2;
+  static constexpr int PAYLOAD = 2 * CODE_BYTES + 4 * META_BYTES;
+  static constexpr int MERGE_BYTES = kHeadsPerCta * D * 4;  // one warp's partial in the epilogue
+  static constexpr int STAGE_BYTES =
+      ((PAYLOAD > MERGE_BYTES ? PAYLOAD : MERGE_BYTES) + 1023) / 1024 * 1024;  // keeps swizzle atoms aligned
   static constexpr uint32_t MASK0 = ((1u << NBITS) - 1u) * 0x00010001u;
   static constexpr int SWZ_SHIFT = (NBLK == 4) ? 1 : 2;
   static_assert(NBLK == 1 || NBLK == 2 || NBLK == 4, "packed row must be 16, 32 or 64 bytes");
   static_assert(GS >= 16 && NG >= 1 && NG <= 8, "group size must be 16..D with at most 8 groups");
 };
 
+// Device-side status word: 0 = ok, 1 = a bounded mbarrier wait gave up.
+__device__ int g_fused_status;
+
 template <int NG>
-__device__ __forceinline__ void load_meta_row(const __half* p, __half (&out)[NG]) {
+struct MetaRow {
+  uint32_t w[(NG + 1) / 2];  // NG halves
+};
+template <int NG>
+__device__ __forceinline__ MetaRow<NG> load_meta_row(const __half* p) {
+  MetaRow<NG> r;
   if constexpr (NG == 8) {
-    *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(p);
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
   } else if constexpr (NG == 4) {
-    *reinterpret_cast<uint2*>(out) = *reinterpret_cast<const uint2*>(p);
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    r.w[0] = v.x; r.w[1] = v.y;
   } else if constexpr (NG == 2) {
-    *reinterpret_cast<uint32_t*>(out) = *reinterpret_cast<const uint32_t*>(p);
+    r.w[0] = *reinterpret_cast<const uint32_t*>(p);
   } else {
-    out[0] = p[0];
+    r.w[0] = *reinterpret_cast<const uint16_t*>(p);
   }
+  return r;
+}
+template <int NG>
+__device__ __forceinline__ float meta_f32(const MetaRow<NG>& r, int i) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&r.w[i >> 1]);
+  return (i & 1) ? __high2float(h) : __low2float(h);
+}
+// {x_i, x_i} as a half2 register operand (folds into the multiply's operand selector)
+template <int NG>
+__device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&r.w[i >> 1]);
+  return (i & 1) ? __high2half2(h) : __low2half2(h);
 }
 
-template <int NBITS, int D, int GS, int STAGES>
-__global__ void __launch_bounds__(128, 3) fused_split_kernel(const DecodeParams p) {
-  using C = FusedCfg<NBITS, D, GS>;
-  constexpr int P = C::P, DP = C::DP, NBLK = C::NBLK, NCH = C::NCH, NG = C::NG;
-  constexpr int NACC = C::NACC, ACC_DIMS = C::ACC_DIMS;
 
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nwarps = blockDim.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int split = blockIdx.x;
-  const int hkv = blockIdx.y / p.hchunks, hc = blockIdx.y % p.hchunks;
-  const int b = blockIdx.z;
+template <int NBITS, int D_, int GS>
+struct FusedPolicy {
+  using C = FusedCfg<NBITS, D_, GS>;
+  static constexpr int D = D_;
+  static constexpr int TOK = kTok;
+  static constexpr int WARPS = 4;
+  static constexpr int STAGES = 2;
+  static constexpr int MIN_CTAS = 4;
+  static constexpr int STAGE_BYTES = C::STAGE_BYTES;
+  static constexpr int P = C::P, DP = C::DP, NBLK = C::NBLK, NCH = C::NCH, NG = C::NG;
+  static constexpr int NACC = C::NACC, ACC_DIMS = C::ACC_DIMS;
 
-  const int S_b = p.seq_lens ? min(max(p.seq_lens[b], 0), p.S) : p.S;
-  const int lo = split * p.split_size;
-  const int hi = min(lo + p.split_size, S_b);
-  const int ntiles = hi > lo ? (hi - lo + kTile - 1) / kTile : 0;
-  const int my_tiles = ntiles > warp ? (ntiles - warp + nwarps - 1) / nwarps : 0;
-  const int64_t row0 = ((int64_t)b * p.HKV + hkv) * p.S;
-
-  // ---- query fragments (B operand of the score MMA) and per-group query sums ----
-  const int head = hc * kHeadsPerCta + g;
-  const bool head_ok = head < p.group;
-  const int64_t qoff = ((int64_t)b * p.HQ + (int64_t)hkv * p.group + head) * D;
-  uint32_t qf[NCH][2];
-  float gsum[NG];
-#pragma unroll
-  for (int i = 0; i < NG; ++i) gsum[i] = 0.f;
-#pragma unroll
-  for (int ch = 0; ch < NCH; ++ch) {
-    __half x[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      x[i] = head_ok ? load_q_half(p.q, p.q_dtype, qoff + 16 * ch + 4 * t + i) : __float2half(0.f);
-    qf[ch][0] = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
-    qf[ch][1] = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
-    gsum[(16 * ch) / GS] += (__half2float(x[0]) + __half2float(x[1])) +
-                            (__half2float(x[2]) + __half2float(x[3]));
-  }
-#pragma unroll
-  for (int i = 0; i < NG; ++i) {
-    gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 1);
-    gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 2);
-  }
-  // B operand of the K zero-point MMA: k-slots (2t, 2t+1) carry the f16 hi/lo split of
-  // the query sum of group t, k-slots (2t+8, 2t+9) that of group t+4.
-  uint32_t qz0 = 0, qz1 = 0;
-#pragma unroll
-  for (int i = 0; i < NG; ++i) {
-    const __half hi16 = __float2half_rn(gsum[i]);
-    const __half lo16 = __float2half_rn(gsum[i] - __half2float(hi16));
-    const uint32_t v = pack_half2(hi16, lo16);
-    if (i == t) qz0 = v;
-    if (i == t + 4) qz1 = v;
-  }
-
-  // ---- per-warp ring ----
-  uint8_t* ring = smem + (size_t)warp * STAGES * C::STAGE_BYTES;
-  const uint32_t ring_u32 = smem_u32(ring);
-  const uint8_t* kp_row = p.kp + row0 * DP;
-  const uint8_t* vp_row = p.vp + row0 * DP;
-  const __half* meta_row[4] = {p.ks + row0 * NG, p.kz + row0 * NG, p.vs + row0 * NG,
-                               p.vz + row0 * NG};
-
-  auto issue = [&](int j) {
-    const int slot = j % STAGES;
-    const int tok0 = lo + (warp + j * nwarps) * kTile;
-    const int nvalid = min(kTile, hi - tok0);
-    const uint32_t st = ring_u32 + slot * C::STAGE_BYTES;
-    constexpr int NCC = kTile * NBLK;  // 16-byte chunks per code tile
-#pragma unroll
-    for (int i0 = 0; i0 < NCC; i0 += 32) {
-      const int i = i0 + lane;
-      if (NCC >= 32 || i < NCC) {
-        const int r = i / NBLK, blk = i % NBLK;
-        const int swz = (NBLK > 1) ? ((r >> C::SWZ_SHIFT) & (NBLK - 1)) : 0;
-        const uint32_t dst = r * DP + ((blk ^ swz) << 4);
-        const bool ok = r < nvalid;
-        const int64_t src = (int64_t)tok0 * DP + i * 16;
-        cp_async16(st + dst, ok ? kp_row + src : p.kp, ok ? 16 : 0);
-        cp_async16(st + C::CODE_BYTES + dst, ok ? vp_row + src : p.vp, ok ? 16 : 0);
-      }
-    }
-    const uint32_t mst = st + 2 * C::CODE_BYTES;
-    if (p.meta_aligned) {
-      constexpr int CPA = C::META_BYTES / 16;   // chunks per metadata array
-      constexpr int TOK_BYTES = NG * 2;         // metadata bytes per token
-#pragma unroll
-      for (int i0 = 0; i0 < 4 * CPA; i0 += 32) {
-        const int i = i0 + lane;
-        if (4 * CPA >= 32 || i < 4 * CPA) {
-          const int arr = i / CPA, c = i % CPA;
-          const int valid_bytes = max(0, min(16, nvalid * TOK_BYTES - c * 16));
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(meta_row[arr]) +
-                               (int64_t)tok0 * TOK_BYTES + c * 16;
-          cp_async16(mst + i * 16, valid_bytes > 0 ? src : (const uint8_t*)p.ks, valid_bytes);
-        }
-      }
-    } else {
-      // Rows that do not start on 16-byte boundaries (odd history lengths): plain loads.
-      __half* dstm = reinterpret_cast<__half*>(ring + slot * C::STAGE_BYTES + 2 * C::CODE_BYTES);
-#pragma unroll
-      for (int arr = 0; arr < 4; ++arr)
-        for (int i = lane; i < kTile * NG; i += 32) {
-          const int tok = i / NG;
-          dstm[arr * kTile * NG + i] =
-              tok < nvalid ? meta_row[arr][(int64_t)tok0 * NG + i] : __float2half(0.f);
-        }
-    }
+  struct Maps {
+    CUtensorMap k, v;
+  };
+  struct Query {
+    uint32_t qf[NCH][2];  // B operand of the score MMA
+    uint32_t qz0, qz1;    // B operand of the K zero-point MMA (hi/lo split of the group sums of q)
+    uint32_t off[2][C::NPAIR];  // this lane's ldmatrix byte offsets inside a code tile
+  };
+  struct Accum {
+    float m_ref0, m_ref1;    // exponent the probabilities refer to
+    float m_true0, m_true1;  // true running maxima
+    float l0, l1;            // per-lane partial sums of p
+    float acc[NCH][4];
+    float zacc[4];
   };
 
-  // ---- running state ----
-  SoftmaxState sm_state{-INFINITY, -INFINITY, 0.f, 0.f};
-  float acc[NCH][4];
-  float zacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[ch][i] = 0.f;
+  __device__ static void report_timeout() { atomicExch(&g_fused_status, 1); }
 
-  const int lm_r = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row this lane addresses
-  const int lm_b = lane >> 4;                           // column-block offset (x4 only)
-  const int lm_swz = (NBLK > 1) ? ((lm_r >> C::SWZ_SHIFT) & (NBLK - 1)) : 0;
-  const uint32_t lm_row_off = lm_r * DP;
-
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < my_tiles) issue(s);
-    cp_async_commit();
+  // Fill one stage with the 32 tokens starting at global row `row`; `nvalid` of them
+  // belong to the unit.
+  __device__ static __forceinline__ void issue(const DecodeParams& p, const Maps& maps, int64_t row,
+                                               int nvalid, uint32_t st, uint8_t* st_ptr,
+                                               uint32_t bar, int lane) {
+    const bool bulk_meta = p.meta_aligned && nvalid == kTok;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar, 2 * kTok * DP + (bulk_meta ? 4 * C::META_BYTES : 0));
+      // wide view: the tensor is [bytes/128, 128]; narrow view: [tokens, DP]
+      const int c1 = p.wide ? (int)((row * DP) >> 7) : (int)row;
+      if (p.exp == 4) {  // experiment: untiled bulk copies for the codes (layout is then unswizzled)
+        bulk_load_1d(st, p.kp + row * DP, kTok * DP, bar);
+        bulk_load_1d(st + C::CODE_BYTES, p.vp + row * DP, kTok * DP, bar);
+      } else {
+        tma_load_2d(st, &maps.k, 0, c1, bar);
+        tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
+      }
+      if (bulk_meta) {
+        const uint32_t mst = st + 2 * C::CODE_BYTES;
+        const int64_t off = row * NG;
+        bulk_load_1d(mst, p.ks + off, C::META_BYTES, bar);
+        bulk_load_1d(mst + C::META_BYTES, p.kz + off, C::META_BYTES, bar);
+        bulk_load_1d(mst + 2 * C::META_BYTES, p.vs + off, C::META_BYTES, bar);
+        bulk_load_1d(mst + 3 * C::META_BYTES, p.vz + off, C::META_BYTES, bar);
+      }
+    }
+    if (!bulk_meta) {
+      // ragged tail or unaligned rows: plain loads; tokens past the end get scale = zero = 0
+      __half* dstm = reinterpret_cast<__half*>(st_ptr + 2 * C::CODE_BYTES);
+      const int64_t off = row * NG;
+      const __half zero = __float2half(0.f);
+      for (int i = lane; i < kTok * NG; i += 32) {
+        const bool ok = (i / NG) < nvalid;
+        dstm[i] = ok ? p.ks[off + i] : zero;
+        dstm[kTok * NG + i] = ok ? p.kz[off + i] : zero;
+        dstm[2 * kTok * NG + i] = ok ? p.vs[off + i] : zero;
+        dstm[3 * kTok * NG + i] = ok ? p.vz[off + i] : zero;
+      }
+    }
   }
 
-  for (int j = 0; j < my_tiles; ++j) {
-    cp_async_wait<STAGES - 2>();
-    __syncwarp();
-    if (j + STAGES - 1 < my_tiles) issue(j + STAGES - 1);
-    cp_async_commit();
+  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p, int b, int hkv,
+                                                    int hc, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    {
+      // ldmatrix addressing: lane l supplies the row address of matrix l/8, row l%8;
+      // matrices are (tokens 0-7, blk), (tokens 8-15, blk), (tokens 0-7, blk+1), (tokens 8-15, blk+1).
+      const int lm_r = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int lm_b = (NBLK >= 2) ? (lane >> 4) : 0;
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int pr = 0; pr < C::NPAIR; ++pr) {
+          const int n = 16 * mt + lm_r, blk = 2 * pr + lm_b;
+          const int L = n * NBLK + blk;  // linear 16-byte chunk index inside the tile
+          int Ls;
+          if (p.wide) {
+            Ls = (L & ~7) | ((L ^ (L >> 3)) & 7);                       // 128B swizzle
+          } else {
+            const int swz = (NBLK > 1) ? ((n >> C::SWZ_SHIFT) & (NBLK - 1)) : 0;
+            Ls = n * NBLK + (blk ^ swz);                                // 32B / 64B swizzle
+          }
+          qq.off[mt][pr] = Ls << 4;
+        }
+    }
+    const int head = hc * kHeadsPerCta + g;
+    const bool head_ok = head < p.group;
+    const int64_t qoff = ((int64_t)b * p.HQ + (int64_t)hkv * p.group + head) * D;
+    float gsum[NG];
+#pragma unroll
+    for (int i = 0; i < NG; ++i) gsum[i] = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      __half x[4];
+      if (p.q_dtype == TKV_DTYPE_F16) {
+        uint2 v = make_uint2(0u, 0u);
+        if (head_ok)
+          v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.q) + qoff +
+                                                   16 * ch + 4 * t));
+        *reinterpret_cast<uint2*>(x) = v;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          x[i] = head_ok ? load_q_half(p.q, p.q_dtype, qoff + 16 * ch + 4 * t + i)
+                         : __float2half(0.f);
+      }
+      qq.qf[ch][0] = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
+      qq.qf[ch][1] = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
+      gsum[(16 * ch) / GS] += (__half2float(x[0]) + __half2float(x[1])) +
+                              (__half2float(x[2]) + __half2float(x[3]));
+    }
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+      gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 1);
+      gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 2);
+    }
+    // k-slots (2t, 2t+1) carry the f16 hi/lo split of the query sum of group t,
+    // k-slots (2t+8, 2t+9) that of group t+4.
+    qq.qz0 = 0;
+    qq.qz1 = 0;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+      const __half hi16 = __float2half_rn(gsum[i]);
+      const __half lo16 = __float2half_rn(gsum[i] - __half2float(hi16));
+      const uint32_t v = pack_half2(hi16, lo16);
+      if (i == t) qq.qz0 = v;
+      if (i == t + 4) qq.qz1 = v;
+    }
+  }
 
-    const int slot = j % STAGES;
-    const int tok0 = lo + (warp + j * nwarps) * kTile;
-    const int nvalid = hi - tok0;  // >= 1; may exceed 16
-    const uint32_t kc = ring_u32 + slot * C::STAGE_BYTES;
+  __device__ static __forceinline__ void reset(Accum& ac) {
+    ac.m_ref0 = ac.m_ref1 = ac.m_true0 = ac.m_true1 = -INFINITY;
+    ac.l0 = ac.l1 = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ac.acc[ch][i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ac.zacc[i] = 0.f;
+  }
+
+  // One 32-token tile in stage `st`; `left` = tokens from the tile start to the unit end.
+  __device__ static __forceinline__ void compute(Accum& ac, const Query& qq, uint32_t st,
+                                                 const uint8_t* st_ptr, int left, float qk_scale,
+                                                 int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t kc = st;
     const uint32_t vc = kc + C::CODE_BYTES;
-    const __half* ks_s = reinterpret_cast<const __half*>(ring + slot * C::STAGE_BYTES + 2 * C::CODE_BYTES);
-    const __half* kz_s = ks_s + kTile * NG;
-    const __half* vs_s = kz_s + kTile * NG;
-    const __half* vz_s = vs_s + kTile * NG;
+    const __half* ks_s = reinterpret_cast<const __half*>(st_ptr + 2 * C::CODE_BYTES);
+    const __half* kz_s = ks_s + kTok * NG;
+    const __half* vs_s = kz_s + kTok * NG;
+    const __half* vz_s = vs_s + kTok * NG;
 
-    // ================= scores: S^T = K Q^T, one accumulator per (slice, group) ========
+  // ================= scores for the two 16-token halves ============================
+  float sc[2][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
     float c[NACC][4];
 #pragma unroll
     for (int a = 0; a < NACC; ++a)
@@ -219,9 +279,9 @@ __global__ void __launch_bounds__(128, 3) fused_split_kernel(const DecodeParams 
     for (int bb = 0; bb < NBLK; bb += 2) {
       uint32_t r[4];
       if constexpr (NBLK >= 2) {
-        ldmatrix_x4(r, kc + lm_row_off + (((bb + lm_b) ^ lm_swz) << 4));
+        ldmatrix_x4(r, kc + qq.off[mt][bb >> 1]);
       } else {
-        ldmatrix_x2(r[0], r[1], kc + lm_row_off);
+        ldmatrix_x2(r[0], r[1], kc + qq.off[mt][0]);
         r[2] = r[3] = 0;
       }
 #pragma unroll
@@ -235,97 +295,134 @@ __global__ void __launch_bounds__(128, 3) fused_split_kernel(const DecodeParams 
           const uint32_t mask = M0 << (NBITS * pp);
           const int ch = pp * NBLK + blk;
           mma16816(c[(16 * ch) / ACC_DIMS], xl & mask, xh & mask, xl8 & mask, xh8 & mask,
-                   qf[ch][0], qf[ch][1]);
+                   qq.qf[ch][0], qq.qf[ch][1]);
         }
       }
     }
     // zero-point term: sum_g z[token][g] * qsum[g][head]
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
     {
+      const __half* kz_t = kz_s + mt * 16 * NG;
       uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
       if (t < NG) {
-        const __half z0 = kz_s[g * NG + t], z1 = kz_s[(g + 8) * NG + t];
+        const __half z0 = kz_t[g * NG + t], z1 = kz_t[(g + 8) * NG + t];
         a0 = pack_half2(z0, z0);
         a1 = pack_half2(z1, z1);
       }
-      if (NG == 8) {
-        const __half z0 = kz_s[g * NG + (t + 4) % NG], z1 = kz_s[(g + 8) * NG + (t + 4) % NG];
+      if constexpr (NG == 8) {
+        const __half z0 = kz_t[g * NG + t + 4], z1 = kz_t[(g + 8) * NG + t + 4];
         a2 = pack_half2(z0, z0);
         a3 = pack_half2(z1, z1);
       }
-      mma16816(sc, a0, a1, a2, a3, qz0, qz1);
+      mma16816(s4, a0, a1, a2, a3, qq.qz0, qq.qz1);
     }
     // scale term
     {
-      __half s_lo[NG], s_hi[NG];
-      load_meta_row<NG>(ks_s + g * NG, s_lo);
-      load_meta_row<NG>(ks_s + (g + 8) * NG, s_hi);
+      const MetaRow<NG> s_lo = load_meta_row<NG>(ks_s + (mt * 16 + g) * NG);
+      const MetaRow<NG> s_hi = load_meta_row<NG>(ks_s + (mt * 16 + g + 8) * NG);
 #pragma unroll
       for (int a = 0; a < NACC; ++a) {
         const int grp = (a * ACC_DIMS) / GS;
         const int slice = (a * ACC_DIMS) / DP;
         const float e = pow2i(24 - NBITS * slice);
-        const float f_lo = __half2float(s_lo[grp]) * e;
-        const float f_hi = __half2float(s_hi[grp]) * e;
-        sc[0] = fmaf(c[a][0], f_lo, sc[0]);
-        sc[1] = fmaf(c[a][1], f_lo, sc[1]);
-        sc[2] = fmaf(c[a][2], f_hi, sc[2]);
-        sc[3] = fmaf(c[a][3], f_hi, sc[3]);
+        const float f_lo = meta_f32<NG>(s_lo, grp) * e;
+        const float f_hi = meta_f32<NG>(s_hi, grp) * e;
+        s4[0] = fmaf(c[a][0], f_lo, s4[0]);
+        s4[1] = fmaf(c[a][1], f_lo, s4[1]);
+        s4[2] = fmaf(c[a][2], f_hi, s4[2]);
+        s4[3] = fmaf(c[a][3], f_hi, s4[3]);
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sc[i] *= p.qk_scale;
-    if (nvalid < kTile) {
-      if (g >= nvalid) sc[0] = sc[1] = -INFINITY;
-      if (g + 8 >= nvalid) sc[2] = sc[3] = -INFINITY;
+    for (int i = 0; i < 4; ++i) sc[mt][i] = s4[i] * qk_scale;
+  }
+  if (left < kTok) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      if (mt * 16 + g >= left) sc[mt][0] = sc[mt][1] = -INFINITY;
+      if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
     }
+  }
 
-    // ================= online softmax ===============================================
-    float alpha0, alpha1;
-    if (softmax_update(sm_state, sc, alpha0, alpha1)) {
+  // ================= online softmax with a lazily raised reference exponent ========
+  {
+    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+    float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+#pragma unroll
+    for (int off = 4; off <= 16; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, off));
+    }
+    ac.m_true0 = fmaxf(ac.m_true0, mx0);
+    ac.m_true1 = fmaxf(ac.m_true1, mx1);
+    if (__any_sync(kFullMask, (mx0 > ac.m_ref0) || (mx1 > ac.m_ref1))) {
+      const float n0 = (mx0 > ac.m_ref0) ? mx0 + kLazyTau : ac.m_ref0;
+      const float n1 = (mx1 > ac.m_ref1) ? mx1 + kLazyTau : ac.m_ref1;
+      const float alpha0 = ex2(ac.m_ref0 - n0);  // first tile: 2^(-inf) = 0; unchanged: 1
+      const float alpha1 = ex2(ac.m_ref1 - n1);
+      ac.m_ref0 = n0;
+      ac.m_ref1 = n1;
+      ac.l0 *= alpha0;
+      ac.l1 *= alpha1;
 #pragma unroll
       for (int ch = 0; ch < NCH; ++ch) {
-        acc[ch][0] *= alpha0;
-        acc[ch][1] *= alpha1;
-        acc[ch][2] *= alpha0;
-        acc[ch][3] *= alpha1;
+        ac.acc[ch][0] *= alpha0;
+        ac.acc[ch][1] *= alpha1;
+        ac.acc[ch][2] *= alpha0;
+        ac.acc[ch][3] *= alpha1;
       }
-      zacc[0] *= alpha0;
-      zacc[1] *= alpha1;
+      ac.zacc[0] *= alpha0;
+      ac.zacc[1] *= alpha1;
     }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      sc[mt][0] = ex2(sc[mt][0] - ac.m_ref0);
+      sc[mt][1] = ex2(sc[mt][1] - ac.m_ref1);
+      sc[mt][2] = ex2(sc[mt][2] - ac.m_ref0);
+      sc[mt][3] = ex2(sc[mt][3] - ac.m_ref1);
+      ac.l0 += sc[mt][0] + sc[mt][2];
+      ac.l1 += sc[mt][1] + sc[mt][3];
+    }
+  }
 
-    // ================= output: O^T += V^T P^T ========================================
-    const uint32_t ph_lo = pack_half2(sc[0], sc[1]);  // token g,   heads 2t, 2t+1
-    const uint32_t ph_hi = pack_half2(sc[2], sc[3]);  // token g+8
+  // ================= output: O^T += V^T P^T ========================================
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+    const uint32_t ph_lo = pack_half2(sc[mt][0], sc[mt][1]);  // token g,   heads 2t, 2t+1
+    const uint32_t ph_hi = pack_half2(sc[mt][2], sc[mt][3]);  // token g+8
     {
       // zero-point term: rows = groups, k = tokens; B = unscaled P^T
       const uint32_t pz0 = movmatrix_trans(ph_lo);
       const uint32_t pz1 = movmatrix_trans(ph_hi);
+      const __half* vz_t = vz_s + mt * 16 * NG;
       uint32_t a0 = 0, a2 = 0;
       if (g < NG) {
-        a0 = pack_half2(vz_s[(2 * t) * NG + g], vz_s[(2 * t + 1) * NG + g]);
-        a2 = pack_half2(vz_s[(2 * t + 8) * NG + g], vz_s[(2 * t + 9) * NG + g]);
+        a0 = pack_half2(vz_t[(2 * t) * NG + g], vz_t[(2 * t + 1) * NG + g]);
+        a2 = pack_half2(vz_t[(2 * t + 8) * NG + g], vz_t[(2 * t + 9) * NG + g]);
       }
-      mma16816(zacc, a0, 0u, a2, 0u, pz0, pz1);
+      mma16816(ac.zacc, a0, 0u, a2, 0u, pz0, pz1);
     }
     uint32_t pb[NG][2];
     {
-      __half s_lo[NG], s_hi[NG];
-      load_meta_row<NG>(vs_s + g * NG, s_lo);
-      load_meta_row<NG>(vs_s + (g + 8) * NG, s_hi);
+      const MetaRow<NG> s_lo = load_meta_row<NG>(vs_s + (mt * 16 + g) * NG);
+      const MetaRow<NG> s_hi = load_meta_row<NG>(vs_s + (mt * 16 + g + 8) * NG);
+      const __half2 p_lo = *reinterpret_cast<const __half2*>(&ph_lo);
+      const __half2 p_hi = *reinterpret_cast<const __half2*>(&ph_hi);
 #pragma unroll
       for (int grp = 0; grp < NG; ++grp) {
-        pb[grp][0] = movmatrix_trans(hmul2_u32(ph_lo, pack_half2(s_lo[grp], s_lo[grp])));
-        pb[grp][1] = movmatrix_trans(hmul2_u32(ph_hi, pack_half2(s_hi[grp], s_hi[grp])));
+        const __half2 a = __hmul2(p_lo, meta_bcast<NG>(s_lo, grp));
+        const __half2 bq = __hmul2(p_hi, meta_bcast<NG>(s_hi, grp));
+        pb[grp][0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&a));
+        pb[grp][1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&bq));
       }
     }
 #pragma unroll
     for (int bb = 0; bb < NBLK; bb += 2) {
       uint32_t r[4];
       if constexpr (NBLK >= 2) {
-        ldmatrix_x4_trans(r, vc + lm_row_off + (((bb + lm_b) ^ lm_swz) << 4));
+        ldmatrix_x4_trans(r, vc + qq.off[mt][bb >> 1]);
       } else {
-        ldmatrix_x2_trans(r[0], r[1], vc + lm_row_off);
+        ldmatrix_x2_trans(r[0], r[1], vc + qq.off[mt][0]);
         r[2] = r[3] = 0;
       }
 #pragma unroll
@@ -339,94 +436,50 @@ __global__ void __launch_bounds__(128, 3) fused_split_kernel(const DecodeParams 
           const uint32_t mask = M0 << (NBITS * pp);
           const int ch = pp * NBLK + blk;
           const int grp = (16 * ch) / GS;
-          mma16816(acc[ch], xl & mask, xl8 & mask, xh & mask, xh8 & mask, pb[grp][0],
+          mma16816(ac.acc[ch], xl & mask, xl8 & mask, xh & mask, xh8 & mask, pb[grp][0],
                    pb[grp][1]);
         }
       }
     }
   }
-  cp_async_wait<0>();
+  }
 
-  // ---- epilogue: finish the warp's values, merge the warps, store ----
+  // Reduce the warp's state, convert it from the reference exponent to the true
+  // maximum (the partial format has m = max) and write vals[head][dim] (8 x D floats).
+  __device__ static __forceinline__ void finalize(Accum& ac, float* vals, SoftmaxState& st,
+                                                  int lane) {
+    const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-  for (int off = 4; off <= 16; off <<= 1) {
-    sm_state.l0 += __shfl_xor_sync(kFullMask, sm_state.l0, off);
-    sm_state.l1 += __shfl_xor_sync(kFullMask, sm_state.l1, off);
-  }
-  __syncthreads();  // every warp is done with its ring before it is reused
-  float* vals = merge_vals<D>(smem, warp);
-#pragma unroll
-  for (int ch = 0; ch < NCH; ++ch) {
-    const int grp = (16 * ch) / GS;
-    const int slice = (16 * ch) / DP;
-    const float e = pow2i(24 - NBITS * slice);
-    const float z0 = __shfl_sync(kFullMask, zacc[0], grp * 4 + t);
-    const float z1 = __shfl_sync(kFullMask, zacc[1], grp * 4 + t);
-    // rows g / g+8 of the output tile are dims 16ch+2g / 16ch+2g+1
-    float2 h0 = make_float2(fmaf(acc[ch][0], e, z0), fmaf(acc[ch][2], e, z0));
-    float2 h1 = make_float2(fmaf(acc[ch][1], e, z1), fmaf(acc[ch][3], e, z1));
-    *reinterpret_cast<float2*>(&vals[(2 * t) * D + 16 * ch + 2 * g]) = h0;
-    *reinterpret_cast<float2*>(&vals[(2 * t + 1) * D + 16 * ch + 2 * g]) = h1;
-  }
-  publish_ml<D>(smem, nwarps, warp, lane, sm_state);
-  __syncthreads();
-  cta_merge_store<D>(p, smem, nwarps, b, hkv, hc, split);
-}
-
-// ------------------------------------------------------------------ host side
-constexpr int kFusedWarps = 4;
-constexpr int kFusedStages = 6;
-
-template <int NBITS, int D, int GS>
-struct FusedLaunch {
-  static constexpr int STAGES = kFusedStages;
-  static int smem_bytes() {
-    const int ring = kFusedWarps * STAGES * FusedCfg<NBITS, D, GS>::STAGE_BYTES;
-    const int merge = merge_bytes<D>(kFusedWarps);
-    return ring > merge ? ring : merge;
-  }
-  static const void* fn() {
-    return reinterpret_cast<const void*>(&fused_split_kernel<NBITS, D, GS, STAGES>);
-  }
-  static int prepare() {
-    static bool done[64] = {};
-    int dev = 0;
-    TKV_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && done[dev]) return TKV_OK;
-    TKV_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
-    if (dev < 64) done[dev] = true;
-    return TKV_OK;
-  }
-  static int launch(const DecodeParams& p, cudaStream_t stream) {
-    int rc = prepare();
-    if (rc != TKV_OK) return rc;
-    dim3 grid(p.num_splits, p.HKV * p.hchunks, p.B);
-    fused_split_kernel<NBITS, D, GS, STAGES><<<grid, kFusedWarps * 32, smem_bytes(), stream>>>(p);
-    TKV_CUDA(cudaGetLastError());
-    return TKV_OK;
-  }
-  static int attrs(int* regs, int* smem, int* local, int* ctas) {
-    int rc = prepare();
-    if (rc != TKV_OK) return rc;
-    cudaFuncAttributes a;
-    TKV_CUDA(cudaFuncGetAttributes(&a, fn()));
-    if (regs) *regs = a.numRegs;
-    if (smem) *smem = (int)a.sharedSizeBytes + smem_bytes();
-    if (local) *local = (int)a.localSizeBytes;
-    if (ctas) {
-      int n = 0;
-      TKV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn(), kFusedWarps * 32,
-                                                             smem_bytes()));
-      *ctas = n;
+    for (int off = 4; off <= 16; off <<= 1) {
+      ac.l0 += __shfl_xor_sync(kFullMask, ac.l0, off);
+      ac.l1 += __shfl_xor_sync(kFullMask, ac.l1, off);
     }
-    return TKV_OK;
+    const float f0 = (ac.m_true0 == -INFINITY) ? 0.f : ex2(ac.m_ref0 - ac.m_true0);
+    const float f1 = (ac.m_true1 == -INFINITY) ? 0.f : ex2(ac.m_ref1 - ac.m_true1);
+    st = SoftmaxState{ac.m_true0, ac.m_true1, ac.l0 * f0, ac.l1 * f1};
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int grp = (16 * ch) / GS;
+      const int slice = (16 * ch) / DP;
+      const float e = pow2i(24 - NBITS * slice);
+      const float z0 = __shfl_sync(kFullMask, ac.zacc[0], grp * 4 + t);
+      const float z1 = __shfl_sync(kFullMask, ac.zacc[1], grp * 4 + t);
+      // rows g / g+8 of the output tile are dims 16ch+2g / 16ch+2g+1
+      float2 h0 = make_float2(fmaf(ac.acc[ch][0], e, z0) * f0, fmaf(ac.acc[ch][2], e, z0) * f0);
+      float2 h1 = make_float2(fmaf(ac.acc[ch][1], e, z1) * f1, fmaf(ac.acc[ch][3], e, z1) * f1);
+      *reinterpret_cast<float2*>(&vals[(2 * t) * D + 16 * ch + 2 * g]) = h0;
+      *reinterpret_cast<float2*>(&vals[(2 * t + 1) * D + 16 * ch + 2 * g]) = h1;
+    }
   }
 };
 
-#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR) \
-  if (nbits == NB && D == DD && gs == GG) {  \
-    using L = FusedLaunch<NB, DD, GG>;       \
-    return EXPR;                             \
+// ------------------------------------------------------------------ host side
+#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)           \
+  if (nbits == NB && D == DD && gs == GG) {            \
+    using L = SplitLaunch<FusedPolicy<NB, DD, GG>>;    \
+    using C = FusedCfg<NB, DD, GG>;                    \
+    (void)sizeof(C);                                   \
+    return EXPR;                                       \
   }
 
 #define TKV_FUSED_ALL(EXPR)             \
@@ -445,18 +498,54 @@ struct FusedLaunch {
   TKV_FUSED_DISPATCH(2, 64, 32, EXPR)   \
   TKV_FUSED_DISPATCH(2, 64, 64, EXPR)
 
-int fused_launch(int nbits, int D, int gs, const DecodeParams& p, cudaStream_t stream) {
-  TKV_FUSED_ALL(L::launch(p, stream))
+static int fused_unsupported(int nbits, int D, int gs) {
   set_error("fused decode: unsupported (nbits=%d, head_dim=%d, group_size=%d); built: nbits in "
             "{2,4}, head_dim in {64,128}, group_size in {16,32,64,128} with group_size <= head_dim",
             nbits, D, gs);
   return TKV_ERR_UNSUPPORTED;
 }
 
+template <class L, class C>
+static int fused_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStream_t stream) {
+  typename FusedPolicy<C::NBITS_, C::D_, C::GS_>::Maps maps;
+  const int64_t rows = (int64_t)p.B * p.HKV * p.S;
+  int rc;
+  if (p.wide) {
+    // [bytes/128, 128] view, box = the 32 tokens' bytes as 128-byte rows, 128B swizzle
+    rc = make_row_map(&maps.k, p.kp, rows * C::DP / 128, 128, 128, kTok * C::DP / 128);
+    if (rc != TKV_OK) return rc;
+    rc = make_row_map(&maps.v, p.vp, rows * C::DP / 128, 128, 128, kTok * C::DP / 128);
+  } else {
+    rc = make_row_map(&maps.k, p.kp, rows, C::DP, C::DP, kTok);
+    if (rc != TKV_OK) return rc;
+    rc = make_row_map(&maps.v, p.vp, rows, C::DP, C::DP, kTok);
+  }
+  if (rc != TKV_OK) return rc;
+  return L::launch(maps, p, sc, stream);
+}
+
+int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
+               int num_splits, int split_size, bool ragged) {
+  TKV_FUSED_ALL(L::plan(sc, B, HKV, hchunks, S, num_splits, split_size, ragged))
+  return fused_unsupported(nbits, D, gs);
+}
+
+static int fused_launch(int nbits, int D, int gs, const DecodeParams& p, const SplitSched& sc,
+                        cudaStream_t stream) {
+  TKV_FUSED_ALL((fused_launch_one<L, C>(p, sc, stream)))
+  return fused_unsupported(nbits, D, gs);
+}
+
 int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int* ctas) {
   TKV_FUSED_ALL(L::attrs(regs, smem, local, ctas))
-  set_error("fused decode: unsupported (nbits=%d, head_dim=%d, group_size=%d)", nbits, D, gs);
-  return TKV_ERR_UNSUPPORTED;
+  return fused_unsupported(nbits, D, gs);
+}
+
+int fused_device_status(int* status) {
+  int v = 0;
+  TKV_CUDA(cudaMemcpyFromSymbol(&v, g_fused_status, sizeof(int)));
+  *status = v;
+  return TKV_OK;
 }
 
 }  // namespace tkv
@@ -466,55 +555,45 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
                                 const void* v_scale, const void* v_zero, float* acc, float* m,
                                 float* l, float* out, int B, int HQ, int HKV, int S, int D,
                                 int nbits, int gs, float sm_scale, int num_splits, int split_size,
-                                const int32_t* seq_lens, int flags, void* stream) {
+                                int nslots, const int32_t* seq_lens, int flags, void* stream) {
   using namespace tkv;
   TKV_REQUIRE(q && k_packed && k_scale && k_zero && v_packed && v_scale && v_zero, TKV_ERR_INVALID,
               "fused decode: null input pointer");
-  TKV_REQUIRE(B > 0 && HQ > 0 && HKV > 0 && S > 0, TKV_ERR_INVALID,
-              "fused decode: B, HQ, HKV, S must be positive (got %d, %d, %d, %d)", B, HQ, HKV, S);
-  TKV_REQUIRE(B <= 65535, TKV_ERR_INVALID, "fused decode: batch %d exceeds 65535", B);
-  TKV_REQUIRE(HQ % HKV == 0, TKV_ERR_INVALID, "HQ=%d must be a multiple of HKV=%d", HQ, HKV);
-  TKV_REQUIRE(q_dtype >= 0 && q_dtype <= 2, TKV_ERR_INVALID, "fused decode: bad q dtype %d", q_dtype);
-  TKV_REQUIRE(num_splits >= 1 && split_size >= 16 && split_size % 16 == 0, TKV_ERR_INVALID,
-              "fused decode: split_size=%d must be a positive multiple of 16, num_splits=%d >= 1",
-              split_size, num_splits);
-  TKV_REQUIRE((int64_t)num_splits * split_size >= S, TKV_ERR_INVALID,
-              "fused decode: %d splits of %d tokens do not cover S=%d", num_splits, split_size, S);
-  const bool partials = num_splits > 1 || (flags & TKV_FLAG_PARTIALS_ONLY);
-  TKV_REQUIRE(!partials || (acc && m && l), TKV_ERR_INVALID,
-              "fused decode: partial buffers (acc, m, l) required");
-  TKV_REQUIRE(partials || out, TKV_ERR_INVALID, "fused decode: out required");
+  DecodeParams p{};
+  int rc = fill_common(p, "fused decode", q, q_dtype, acc, m, l, out, B, HQ, HKV, S, sm_scale,
+                       num_splits, split_size, nslots, seq_lens, flags);
+  if (rc != TKV_OK) return rc;
   TKV_REQUIRE(aligned16(k_packed) && aligned16(v_packed), TKV_ERR_ALIGN,
               "fused decode: packed code pointers must be 16-byte aligned");
-  DecodeParams p{};
-  p.q = q;
-  p.q_dtype = q_dtype;
   p.kp = k_packed;
   p.vp = v_packed;
   p.ks = (const __half*)k_scale;
   p.kz = (const __half*)k_zero;
   p.vs = (const __half*)v_scale;
   p.vz = (const __half*)v_zero;
-  p.acc = acc;
-  p.m = m;
-  p.l = l;
-  p.out = out;
-  p.seq_lens = seq_lens;
-  p.B = B;
-  p.HQ = HQ;
-  p.HKV = HKV;
-  p.S = S;
-  p.group = HQ / HKV;
-  p.hchunks = (p.group + kHeadsPerCta - 1) / kHeadsPerCta;
-  p.num_splits = num_splits;
-  p.split_size = split_size;
-  p.qk_scale = sm_scale * kLog2e;
-  p.partials = partials ? 1 : 0;
-  TKV_REQUIRE((int64_t)HKV * p.hchunks <= 65535, TKV_ERR_INVALID, "fused decode: too many heads");
   const int ng = (gs > 0 && D % gs == 0) ? D / gs : 0;
   p.meta_aligned = (ng > 0 && ((int64_t)S * ng * 2) % 16 == 0 && aligned16(k_scale) &&
                     aligned16(k_zero) && aligned16(v_scale) && aligned16(v_zero))
                        ? 1
                        : 0;
-  return fused_launch(nbits, D, gs, p, (cudaStream_t)stream);
+  // 128-byte-row view of the code tensors: every sequence must start on a 128-byte boundary
+  p.wide = (((int64_t)S * D * nbits / 8) % 128 == 0) ? 1 : 0;
+  static const int no_wide = [] {
+    const char* e = getenv("TKV_NARROW");
+    return e ? atoi(e) : 0;
+  }();
+  if (no_wide) p.wide = 0;
+  static const int exp_mode = [] {
+    const char* e = getenv("TKV_EXP");
+    return e ? atoi(e) : 0;
+  }();
+  p.exp = exp_mode;
+  SplitSched sc;
+  rc = fused_plan(nbits, D, gs, &sc, B, HKV, p.hchunks, S, num_splits, split_size,
+                  seq_lens != nullptr);
+  if (rc != TKV_OK) return rc;
+  TKV_REQUIRE(sc.nslots == nslots, TKV_ERR_INVALID,
+              "fused decode: nslots=%d does not match the plan (%d); size acc/m/l with "
+              "tkv_decode_plan", nslots, sc.nslots);
+  return fused_launch(nbits, D, gs, p, sc, (cudaStream_t)stream);
 }

@@ -1,0 +1,488 @@
+// Persistent, balanced split-K driver shared by the packed-cache kernel and the fp16
+// control kernel (sm_100a).
+//
+// Work model.  A "unit" is one (batch, KV head, head chunk, history split); its tokens
+// are cut into tiles of Policy::TOK tokens.  All tiles of all units form one global sequence.  The
+// grid is one wave of persistent CTAs; CTA c owns the contiguous global tile range
+// [c*TC, (c+1)*TC).  Where that range crosses unit boundaries the CTA processes one
+// "segment" per unit and emits one partial (acc, m, l) per segment, so every CTA does
+// the same number of tiles (+-1) whatever the batch and history sizes are -- no ragged
+// last wave, no per-unit launch cost -- and the reference's split geometry
+// (kernels/fused_decode_attn.py:493-499) survives as the unit boundaries.
+// Partial slot of a segment: split*SEG + (c - first CTA touching the unit); the CTA
+// that finishes a unit marks the unit's unused slots empty (m = -inf).
+//
+// Inside a CTA every warp is an independent stream with a private ring of STAGES
+// shared-memory stages and one mbarrier per stage.  Lane 0 issues the copies of a
+// tile (Policy::issue); the ring keeps running across segment boundaries, so the next
+// unit's first tiles are already in flight while a segment's epilogue runs.  Warps
+// only meet at a segment end: each writes its partial into its one free stage, the
+// CTA merges the warps' partials (log-sum-exp) and stores the segment's partial or,
+// when a unit has a single slot, the normalised output.
+//
+// With per-sequence lengths (seq_lens) the schedule is static instead: CTA c <-> unit c.
+#pragma once
+
+#include <cuda.h>
+
+#include "tkv_split_common.cuh"
+
+namespace tkv {
+
+constexpr float kLazyTau = 4.0f;  // head-room of the lazily raised softmax exponent (log2 units)
+
+struct SplitSched {
+  int persistent;  // 1: balanced tile ranges; 0: CTA c <-> unit c (ragged batches)
+  int NS;          // history splits per sequence (unit boundaries)
+  int TUf, TUl;    // tiles in a full split / in the last split
+  int T_seq;       // tiles per sequence = (NS-1)*TUf + TUl
+  int T;           // total tiles
+  int TC;          // tiles per CTA
+  int SEG;         // partial slots per split
+  int nslots;      // NS * SEG
+  int grid;        // CTAs
+  int HKVc;        // HKV * head chunks
+};
+
+inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits, int split_size,
+                             bool ragged, int wave, int kTok) {
+  SplitSched s{};
+  s.NS = num_splits;
+  s.HKVc = HKV * hchunks;
+  const int last_len = S - (num_splits - 1) * split_size;
+  s.TUf = (num_splits > 1 ? split_size : S) > 0 ? ((num_splits > 1 ? split_size : S) + kTok - 1) / kTok : 0;
+  s.TUl = (last_len + kTok - 1) / kTok;
+  if (num_splits == 1) s.TUf = s.TUl;
+  s.T_seq = (num_splits - 1) * s.TUf + s.TUl;
+  const int64_t units = (int64_t)B * s.HKVc * num_splits;
+  if (ragged) {
+    s.persistent = 0;
+    s.T = 0;
+    s.TC = 0;
+    s.SEG = 1;
+    s.grid = (int)units;
+  } else {
+    s.persistent = 1;
+    const int64_t T = (int64_t)B * s.HKVc * s.T_seq;
+    s.T = (int)T;
+    const int G = (int)(T < wave ? T : wave);
+    s.TC = (int)((T + G - 1) / G);
+    s.grid = (int)((T + s.TC - 1) / s.TC);
+    s.SEG = (s.TUf - 1 + s.TC - 1) / s.TC + 1;
+    if (s.TUf <= 1) s.SEG = 1;
+  }
+  s.nslots = s.NS * s.SEG;
+  return s;
+}
+
+// One segment: the part of one unit that one CTA processes.
+struct Segment {
+  int b, hkv, hc;     // unit coordinates
+  int split;          // history split index
+  int lo_tok;         // first token of the segment (absolute, within the sequence)
+  int hi;             // end of the unit's token range (exclusive)
+  int ntiles;         // tiles in this segment
+  int g_end;          // global tile index one past the segment (persistent mode)
+  int slot;           // partial slot
+  int fill_from;      // if >= 0: after the epilogue mark slots [fill_from, fill_to) empty
+  int fill_to;
+};
+
+template <int kTok>
+__device__ __forceinline__ Segment segment_at(const DecodeParams& p, const SplitSched& sc, int g,
+                                              int g1, int cta) {
+  Segment s;
+  const int bh = g / sc.T_seq;
+  const int r = g - bh * sc.T_seq;
+  const int sp = min(r / sc.TUf, sc.NS - 1);
+  const int tu = r - sp * sc.TUf;
+  const int TU = (sp == sc.NS - 1) ? sc.TUl : sc.TUf;
+  const int unit_start = bh * sc.T_seq + sp * sc.TUf;
+  const int unit_end = unit_start + TU;
+  s.b = bh / sc.HKVc;
+  const int hk = bh - s.b * sc.HKVc;
+  s.hkv = hk / p.hchunks;
+  s.hc = hk - s.hkv * p.hchunks;
+  s.split = sp;
+  const int lo_unit = sp * p.split_size;
+  s.hi = min(lo_unit + p.split_size, p.S);
+  s.lo_tok = lo_unit + tu * kTok;
+  s.g_end = min(g1, unit_end);
+  s.ntiles = s.g_end - g;
+  const int c_first = unit_start / sc.TC;
+  const int seg = cta - c_first;
+  s.slot = sp * sc.SEG + seg;
+  if (s.g_end == unit_end && seg + 1 < sc.SEG) {
+    s.fill_from = s.slot + 1;
+    s.fill_to = sp * sc.SEG + sc.SEG;
+  } else {
+    s.fill_from = -1;
+    s.fill_to = -1;
+  }
+  return s;
+}
+
+// Per-warp cursor over the tiles this warp will issue, possibly segments ahead.
+struct IssueCursor {
+  int seg_g;      // global tile index where the cursor's segment starts (persistent mode)
+  int64_t row;    // global row (token index over the whole cache tensor) of the next tile
+  int left;       // tokens from the next tile's first token to the end of its unit
+  int cnt;        // tiles this warp still has to issue in the cursor's segment
+  int g_end;      // end of the cursor's segment
+};
+
+template <class Policy>
+__global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
+    splitk_kernel(const __grid_constant__ typename Policy::Maps maps, const DecodeParams p,
+                  const SplitSched sc) {
+  constexpr int WARPS = Policy::WARPS, STAGES = Policy::STAGES, D = Policy::D;
+  constexpr int kTok = Policy::TOK;
+  constexpr int STAGE_BYTES = Policy::STAGE_BYTES;
+  static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte alignment");
+  static_assert(STAGE_BYTES >= kHeadsPerCta * D * 4, "a stage must hold one warp's partial");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  __shared__ float s_m[WARPS][kHeadsPerCta];
+  __shared__ float s_l[WARPS][kHeadsPerCta];
+  __shared__ int s_slot[WARPS];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+
+  uint8_t* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
+  const uint32_t ring_u32 = smem_u32(ring);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)WARPS * STAGES * STAGE_BYTES);
+  const uint32_t bar_u32 = smem_u32(bars + warp * STAGES);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + 8 * s, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+
+  // ---- this CTA's tile range ----
+  int g0, g1;
+  Segment seg;
+  if (sc.persistent) {
+    g0 = min(cta * sc.TC, sc.T);
+    g1 = min(g0 + sc.TC, sc.T);
+    if (g0 >= g1) return;
+    seg = segment_at<kTok>(p, sc, g0, g1, cta);
+  } else {
+    // static: CTA <-> unit, per-sequence length from seq_lens
+    const int bh = cta / sc.NS;
+    seg.split = cta - bh * sc.NS;
+    seg.b = bh / sc.HKVc;
+    const int hk = bh - seg.b * sc.HKVc;
+    seg.hkv = hk / p.hchunks;
+    seg.hc = hk - seg.hkv * p.hchunks;
+    const int S_b = p.seq_lens ? min(max(p.seq_lens[seg.b], 0), p.S) : p.S;
+    const int lo_unit = seg.split * p.split_size;
+    seg.hi = min(lo_unit + p.split_size, S_b);
+    seg.lo_tok = lo_unit;
+    seg.ntiles = seg.hi > lo_unit ? (seg.hi - lo_unit + kTok - 1) / kTok : 0;
+    seg.slot = seg.split;
+    seg.fill_from = seg.fill_to = -1;
+    g0 = 0;
+    g1 = seg.ntiles;
+    seg.g_end = g1;
+  }
+
+  // ---- issue cursor ----
+  auto cursor_enter = [&](IssueCursor& c, const Segment& s, int seg_g) {
+    c.seg_g = seg_g;
+    c.g_end = s.g_end;
+    c.cnt = s.ntiles > warp ? (s.ntiles - warp + WARPS - 1) / WARPS : 0;
+    const int tok = s.lo_tok + warp * kTok;
+    c.row = ((int64_t)s.b * p.HKV + s.hkv) * p.S + tok;
+    c.left = s.hi - tok;
+  };
+  IssueCursor cur;
+  cursor_enter(cur, seg, g0);
+  auto cursor_skip_empty = [&]() {
+    // move to the next segment in which this warp has a tile (persistent mode only)
+    while (cur.cnt == 0 && sc.persistent && cur.g_end < g1) {
+      const int g = cur.g_end;
+      const Segment s = segment_at<kTok>(p, sc, g, g1, cta);
+      cursor_enter(cur, s, g);
+    }
+  };
+  cursor_skip_empty();
+  int issued = 0;
+  bool need_proxy_fence = false;
+  auto issue_next = [&]() {
+    if (cur.cnt == 0) return;
+    const int slot = issued % STAGES;
+    if (need_proxy_fence) {  // a generic-proxy epilogue touched the ring since the last issue
+      fence_proxy_async();
+      need_proxy_fence = false;
+    }
+    Policy::issue(p, maps, cur.row, min(kTok, cur.left), ring_u32 + slot * STAGE_BYTES,
+                  ring + slot * STAGE_BYTES, bar_u32 + 8 * slot, lane);
+    ++issued;
+    cur.row += WARPS * kTok;
+    cur.left -= WARPS * kTok;
+    --cur.cnt;
+    cursor_skip_empty();
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue_next();
+
+  int consumed = 0;
+  bool timed_out = false;
+  typename Policy::Query qs;
+  typename Policy::Accum acc;
+
+  for (int g = g0;;) {
+    // ---- one segment ----
+    Policy::load_query(qs, p, seg.b, seg.hkv, seg.hc, lane);
+    Policy::reset(acc);
+    const int my_tiles = seg.ntiles > warp ? (seg.ntiles - warp + WARPS - 1) / WARPS : 0;
+    int left = seg.hi - (seg.lo_tok + warp * kTok);
+    for (int i = 0; i < my_tiles && !timed_out; ++i) {
+      const int slot = consumed % STAGES;
+      if (!mbar_wait_bounded(bar_u32 + 8 * slot, (consumed / STAGES) & 1)) {
+        timed_out = true;
+        break;
+      }
+      __syncwarp();
+      issue_next();  // refills the stage consumed in the previous iteration
+      if (p.exp != 2 && p.exp != 4)
+        Policy::compute(acc, qs, ring_u32 + slot * STAGE_BYTES, ring + slot * STAGE_BYTES, left,
+                        p.qk_scale, lane);
+      left -= WARPS * kTok;
+      ++consumed;
+    }
+
+    // ---- segment epilogue: merge the warps, store the partial ----
+    float* vals = reinterpret_cast<float*>(ring + ((consumed + STAGES - 1) % STAGES) * STAGE_BYTES);
+    SoftmaxState st;
+    if (my_tiles > 0) {
+      Policy::finalize(acc, vals, st, lane);  // the stage consumed last is free until the next issue
+    } else {
+      st = SoftmaxState{-INFINITY, -INFINITY, 0.f, 0.f};
+    }
+    if ((lane >> 2) == 0) {
+      const int t = lane & 3;
+      s_m[warp][2 * t] = st.m0;
+      s_m[warp][2 * t + 1] = st.m1;
+      s_l[warp][2 * t] = st.l0;
+      s_l[warp][2 * t + 1] = st.l1;
+    }
+    if (lane == 0) s_slot[warp] = (consumed + STAGES - 1) % STAGES;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < kHeadsPerCta * D; idx += WARPS * 32) {
+      const int h = idx / D, d = idx - h * D;
+      const int hg = seg.hc * kHeadsPerCta + h;
+      if (hg >= p.group) continue;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w][h]);
+      float a = 0.f, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float mw = s_m[w][h];
+        if (mw != -INFINITY) {
+          const float s = ex2(mw - M);
+          const float* v = reinterpret_cast<const float*>(
+              smem + ((size_t)w * STAGES + s_slot[w]) * STAGE_BYTES);
+          a = fmaf(s, v[h * D + d], a);
+          L = fmaf(s, s_l[w][h], L);
+        }
+      }
+      const int64_t hq = (int64_t)seg.b * p.HQ + seg.hkv * p.group + hg;
+      if (p.partials) {
+        const int64_t pi = hq * sc.nslots + seg.slot;
+        p.acc[pi * D + d] = a;
+        if (d == 0) {
+          p.m[pi] = M;
+          p.l[pi] = L;
+        }
+      } else {
+        p.out[hq * D + d] = (L > 0.f) ? a / L : 0.f;
+      }
+    }
+    if (seg.fill_from >= 0) {
+      // this CTA finished the unit: mark the unit's unused partial slots empty
+      const int nfill = seg.fill_to - seg.fill_from;
+      for (int idx = threadIdx.x; idx < kHeadsPerCta * nfill; idx += WARPS * 32) {
+        const int h = idx / nfill, j = idx - h * nfill;
+        const int hg = seg.hc * kHeadsPerCta + h;
+        if (hg < p.group) {
+          const int64_t hq = (int64_t)seg.b * p.HQ + seg.hkv * p.group + hg;
+          p.m[hq * sc.nslots + seg.fill_from + j] = -INFINITY;
+          p.l[hq * sc.nslots + seg.fill_from + j] = 0.f;
+        }
+      }
+    }
+    __syncthreads();
+    need_proxy_fence = true;
+
+    if (!sc.persistent) break;
+    g = seg.g_end;
+    if (g >= g1 || timed_out) break;
+    seg = segment_at<kTok>(p, sc, g, g1, cta);
+  }
+  if (timed_out && lane == 0) Policy::report_timeout();
+}
+
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map over a row-major byte matrix [rows, row_bytes] whose box is
+// [box_rows, box_bytes] starting at byte column c0 (given at load time), with the
+// shared-memory swizzle that makes 8-row x 16-byte ldmatrix blocks conflict free.
+inline int make_row_map(CUtensorMap* tm, const void* base, int64_t rows, int row_bytes,
+                        int box_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  TKV_REQUIRE(fn != nullptr, TKV_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle swz = box_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                 : box_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                   : CU_TENSOR_MAP_SWIZZLE_NONE;
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim,
+                        gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TKV_REQUIRE(r == CUDA_SUCCESS, TKV_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
+              (int)r);
+  return TKV_OK;
+}
+
+template <class Policy>
+struct SplitLaunch {
+  static int smem_bytes() {
+    return Policy::WARPS * Policy::STAGES * Policy::STAGE_BYTES + Policy::WARPS * Policy::STAGES * 8 +
+           1024;  // slack for the 1024-byte alignment of the ring
+  }
+  static const void* fn() { return reinterpret_cast<const void*>(&splitk_kernel<Policy>); }
+  static int prepare() {
+    static bool done[64] = {};
+    int dev = 0;
+    TKV_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && done[dev]) return TKV_OK;
+    TKV_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    if (dev < 64) done[dev] = true;
+    return TKV_OK;
+  }
+  // CTAs resident at once on the current device (one wave of the persistent grid).
+  static int wave(int* out) {
+    static int cached[64] = {};
+    int dev = 0;
+    TKV_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && cached[dev] > 0) {
+      *out = cached[dev];
+      return TKV_OK;
+    }
+    int rc = prepare();
+    if (rc != TKV_OK) return rc;
+    int n = 0, sms = 0;
+    TKV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn(), Policy::WARPS * 32,
+                                                           smem_bytes()));
+    TKV_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    TKV_REQUIRE(n > 0 && sms > 0, TKV_ERR_CUDA, "split kernel does not fit on this device");
+    *out = n * sms;
+    if (dev < 64) cached[dev] = *out;
+    return TKV_OK;
+  }
+  static int plan(SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
+                  int split_size, bool ragged) {
+    int w = 0;
+    int rc = wave(&w);
+    if (rc != TKV_OK) return rc;
+    *sc = make_sched(B, HKV, hchunks, S, num_splits, split_size, ragged, w, Policy::TOK);
+    return TKV_OK;
+  }
+  static int launch(const typename Policy::Maps& maps, const DecodeParams& p, const SplitSched& sc,
+                    cudaStream_t stream) {
+    int rc = prepare();
+    if (rc != TKV_OK) return rc;
+    splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem_bytes(), stream>>>(maps, p, sc);
+    TKV_CUDA(cudaGetLastError());
+    return TKV_OK;
+  }
+  static int attrs(int* regs, int* smem, int* local, int* ctas) {
+    int rc = prepare();
+    if (rc != TKV_OK) return rc;
+    cudaFuncAttributes a;
+    TKV_CUDA(cudaFuncGetAttributes(&a, fn()));
+    if (regs) *regs = a.numRegs;
+    if (smem) *smem = (int)a.sharedSizeBytes + smem_bytes();
+    if (local) *local = (int)a.localSizeBytes;
+    if (ctas) {
+      int n = 0;
+      TKV_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn(), Policy::WARPS * 32,
+                                                             smem_bytes()));
+      *ctas = n;
+    }
+    return TKV_OK;
+  }
+};
+
+// Argument checks and DecodeParams fields shared by the two decode entry points.
+inline int fill_common(DecodeParams& p, const char* who, const void* q, int q_dtype, float* acc,
+                       float* m, float* l, float* out, int B, int HQ, int HKV, int S,
+                       float sm_scale, int num_splits, int split_size, int nslots,
+                       const int32_t* seq_lens, int flags) {
+  TKV_REQUIRE(B > 0 && HQ > 0 && HKV > 0 && S > 0, TKV_ERR_INVALID,
+              "%s: B, HQ, HKV, S must be positive (got %d, %d, %d, %d)", who, B, HQ, HKV, S);
+  TKV_REQUIRE((int64_t)B * HKV * S < (1LL << 31), TKV_ERR_INVALID,
+              "%s: B*HKV*S = %lld cached tokens exceed 2^31", who, (long long)B * HKV * S);
+  TKV_REQUIRE(HQ % HKV == 0, TKV_ERR_INVALID, "HQ=%d must be a multiple of HKV=%d", HQ, HKV);
+  TKV_REQUIRE(q_dtype >= 0 && q_dtype <= 2, TKV_ERR_INVALID, "%s: bad q dtype %d", who, q_dtype);
+  TKV_REQUIRE(num_splits >= 1 && split_size >= 16 && split_size % 16 == 0, TKV_ERR_INVALID,
+              "%s: split_size=%d must be a positive multiple of 16, num_splits=%d >= 1", who,
+              split_size, num_splits);
+  TKV_REQUIRE((int64_t)num_splits * split_size >= S &&
+                  (int64_t)(num_splits - 1) * split_size < S,
+              TKV_ERR_INVALID, "%s: %d splits of %d tokens must cover S=%d with no empty split", who,
+              num_splits, split_size, S);
+  const bool partials = nslots > 1 || (flags & TKV_FLAG_PARTIALS_ONLY);
+  TKV_REQUIRE(!partials || (acc && m && l), TKV_ERR_INVALID,
+              "%s: partial buffers (acc, m, l) required", who);
+  TKV_REQUIRE(partials || out, TKV_ERR_INVALID, "%s: out required", who);
+  TKV_REQUIRE(q_dtype != TKV_DTYPE_F16 || ((uintptr_t)q & 7u) == 0, TKV_ERR_ALIGN,
+              "%s: q must be 8-byte aligned", who);
+  p.q = q;
+  p.q_dtype = q_dtype;
+  p.acc = acc;
+  p.m = m;
+  p.l = l;
+  p.out = out;
+  p.seq_lens = seq_lens;
+  p.B = B;
+  p.HQ = HQ;
+  p.HKV = HKV;
+  p.S = S;
+  p.group = HQ / HKV;
+  p.hchunks = (p.group + kHeadsPerCta - 1) / kHeadsPerCta;
+  p.num_splits = num_splits;
+  p.split_size = split_size;
+  p.qk_scale = sm_scale * kLog2e;
+  p.partials = partials ? 1 : 0;
+  return TKV_OK;
+}
+
+}  // namespace tkv

@@ -34,28 +34,70 @@ def pick_num_splits(B: int, HKV: int, n_blocks: int, target_programs: int | None
     return max(1, min(n_blocks, want))
 
 
+def balanced_num_splits(B: int, HKV: int, n_blocks: int, block_n: int, wave: int,
+                        max_splits: int = 64) -> int:
+    """Number of history splits that minimises the modelled step time on a device
+    that holds ``wave`` CTAs at once.
+
+    The reference fills the device with ``target // (B*HKV)`` splits
+    (kernels/fused_decode_attn.py:402-416), which is right while ``B*HKV`` is far
+    below one wave.  Near or above one wave that rule leaves a ragged last wave
+    (512 CTAs on 444 slots run as two waves, the second 15 % full), so here the
+    split count is chosen by a cost model: waves x (tokens per CTA + a fixed
+    per-CTA cost) plus a per-split cost of the combine pass.
+    """
+    units = max(1, B * HKV)
+    if units * 2 <= wave:  # far below one wave: the reference's rule
+        return pick_num_splits(B, HKV, n_blocks, wave)
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(n_blocks, max_splits)) + 1):
+        bps = cdiv(n_blocks, s)
+        s_eff = cdiv(n_blocks, bps)
+        tokens = bps * block_n
+        waves = cdiv(units * s_eff, wave)
+        cost = waves * (tokens + 160) + 24 * (s_eff if s_eff > 1 else 0)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s_eff, cost
+    return best
+
+
 def split_geometry(S: int, block_n: int, num_splits: int | None, B: int, HKV: int,
-                   target_programs: int | None):
-    """(block_n, num_splits, split_size) with the reference's clamping: block_n is
-    limited to ``max(16, pow2(S))`` and no split is empty."""
+                   target_programs: int | None, ragged: bool = False):
+    """(block_n, num_splits, split_size) with the reference's clamping
+    (kernels/fused_decode_attn.py:487-499): block_n is limited to ``max(16, pow2(S))``,
+    splits are whole multiples of block_n and none is empty.
+
+    ``num_splits=None``: the kernels balance the work themselves (every CTA gets an
+    equal contiguous range of tiles, see ``tkv_decode_plan``), so one split covering
+    the whole history is requested -- except for ragged batches (``seq_lens``), which
+    are scheduled one CTA per (sequence, KV head, split) and therefore get a split
+    count from the cost model, given ``target_programs`` CTAs resident at once.
+    """
     block_n = min(block_n, max(16, next_pow2(S)))
     if block_n < 16 or block_n % 16:
         raise ValueError(f"block_n must be a multiple of 16, got {block_n}")
     n_blocks = cdiv(S, block_n)
     if num_splits is None:
-        num_splits = pick_num_splits(B, HKV, n_blocks, target_programs)
+        if not ragged:
+            num_splits = 1
+        elif target_programs is None:
+            num_splits = pick_num_splits(B, HKV, n_blocks, None)
+        else:
+            num_splits = balanced_num_splits(B, HKV, n_blocks, block_n, target_programs)
     num_splits = max(1, min(num_splits, n_blocks))
     blocks_per_split = cdiv(n_blocks, num_splits)
     num_splits = cdiv(n_blocks, blocks_per_split)  # tighten: no empty splits
     return block_n, num_splits, blocks_per_split * block_n
 
 
-def get_workspace(ws: dict, B: int, HQ: int, num_splits: int, D: int, device, force_partials: bool):
+def get_workspace(ws: dict, B: int, HQ: int, nslots: int, D: int, device, force_partials: bool):
     """Split-partial buffers, reused through the caller's dict exactly as the
     reference does (keys ``key``, ``acc``, ``maxs``, ``sums``, ``dummy_acc``), so a
-    call with ``out`` and ``_workspace`` supplied allocates nothing."""
-    single = num_splits == 1 and not force_partials
-    key = (B, HQ, num_splits, D)
+    call with ``out`` and ``_workspace`` supplied allocates nothing.  ``nslots`` is the
+    number of partials per (batch, head) the split kernel writes; it takes the place
+    of the reference's ``num_splits`` in the key and the buffer shapes."""
+    single = nslots == 1 and not force_partials
+    key = (B, HQ, nslots, D)
     if single:
         acc = ws.get("dummy_acc")
         if acc is None or acc.device != device:
@@ -64,9 +106,9 @@ def get_workspace(ws: dict, B: int, HQ: int, num_splits: int, D: int, device, fo
         return None, None, None
     if ws.get("key") == key and ws["acc"].device == device:
         return ws["acc"], ws["maxs"], ws["sums"]
-    acc = torch.empty((B, HQ, num_splits, D), device=device, dtype=torch.float32)
-    maxs = torch.empty((B, HQ, num_splits), device=device, dtype=torch.float32)
-    sums = torch.empty((B, HQ, num_splits), device=device, dtype=torch.float32)
+    acc = torch.empty((B, HQ, nslots, D), device=device, dtype=torch.float32)
+    maxs = torch.empty((B, HQ, nslots), device=device, dtype=torch.float32)
+    sums = torch.empty((B, HQ, nslots), device=device, dtype=torch.float32)
     ws.update(key=key, acc=acc, maxs=maxs, sums=sums)
     return acc, maxs, sums
 

@@ -59,23 +59,27 @@ def fp16_decode_attention(
 
     lib = _cabi.load()
     with torch.cuda.device(device):
+        ragged = seq_lens is not None
         target = None
-        if num_splits is None:
+        if num_splits is None and ragged:
             target = _cabi.wave_programs(_cabi.KERNEL_FP16_SPLIT, 0, D, 0)
-        block_n, num_splits, split_size = split_geometry(S, block_n, num_splits, B, HKV, target)
+        block_n, num_splits, split_size = split_geometry(S, block_n, num_splits, B, HKV, target,
+                                                         ragged)
+        nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FP16_SPLIT, 0, D, 0, B, HQ, HKV, S, num_splits,
+                                      split_size, ragged)
 
         out = check_out(out, B, HQ, D, device)
         ws = _workspace if _workspace is not None else {}
-        acc, maxs, sums = get_workspace(ws, B, HQ, num_splits, D, device, _partials_only)
+        acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
 
         stream = _cabi.stream_ptr(device)
         flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else 0
         _cabi.check(lib.tkv_fp16_decode(
             q.data_ptr(), _cabi.dtype_code(q), k.data_ptr(), v.data_ptr(),
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
-            B, HQ, HKV, S, D, float(sm_scale), num_splits, split_size,
+            B, HQ, HKV, S, D, float(sm_scale), num_splits, split_size, nslots,
             _cabi.ptr(seq_lens), flags, stream))
         if acc is not None and not _partials_only:
             _cabi.check(lib.tkv_combine(acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(),
-                                        out.data_ptr(), None, None, B, HQ, num_splits, D, stream))
+                                        out.data_ptr(), None, None, B, HQ, nslots, D, stream))
     return out

@@ -56,7 +56,10 @@ def fused_decode_attention(
     ``packed`` of shape ``(B, HKV, S, D//P)``.  Returns ``(B, HQ, D)`` float32.
 
     ``block_n`` and ``num_splits`` set the split geometry as in the reference
-    (splits are whole multiples of ``block_n`` tokens, none empty).  ``num_warps``,
+    (splits are whole multiples of ``block_n`` tokens, none empty); the kernel cuts
+    the splits further into equal per-CTA ranges, so ``num_splits=None`` asks for one
+    split and lets the kernel fill the device, and the workspace holds ``nslots >=
+    num_splits`` partials per head (``_workspace["key"] == (B, HQ, nslots, D)``).  ``num_warps``,
     ``num_stages``, ``meta_bcast`` and ``dequant_fp16`` selected Triton code
     variants that computed identical values; here they are accepted and ignored,
     so results are trivially equal across them.  ``fold_zp`` named the variant that
@@ -102,14 +105,18 @@ def fused_decode_attention(
 
     lib = _cabi.load()
     with torch.cuda.device(device):
+        ragged = seq_lens is not None
         target = None
-        if num_splits is None:
+        if num_splits is None and ragged:
             target = _cabi.wave_programs(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs)
-        block_n, num_splits, split_size = split_geometry(S, block_n, num_splits, B, HKV, target)
+        block_n, num_splits, split_size = split_geometry(S, block_n, num_splits, B, HKV, target,
+                                                         ragged)
+        nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S,
+                                      num_splits, split_size, ragged)
 
         out = check_out(out, B, HQ, D, device)
         ws = _workspace if _workspace is not None else {}
-        acc, maxs, sums = get_workspace(ws, B, HQ, num_splits, D, device, _partials_only)
+        acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
 
         stream = _cabi.stream_ptr(device)
         flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else 0
@@ -118,9 +125,9 @@ def fused_decode_attention(
             kp.data_ptr(), ks.data_ptr(), kz.data_ptr(),
             vp.data_ptr(), vs.data_ptr(), vz.data_ptr(),
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
-            B, HQ, HKV, S, D, nbits, gs, float(sm_scale), num_splits, split_size,
+            B, HQ, HKV, S, D, nbits, gs, float(sm_scale), num_splits, split_size, nslots,
             _cabi.ptr(seq_lens), flags, stream))
         if acc is not None and not _partials_only:
             _cabi.check(lib.tkv_combine(acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(),
-                                        out.data_ptr(), None, None, B, HQ, num_splits, D, stream))
+                                        out.data_ptr(), None, None, B, HQ, nslots, D, stream))
     return out
