@@ -342,7 +342,7 @@ def run_ours(args):
         key = f"{args.workload}/{nbits}b/ctx{S_local}"
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(key),
-                    "peak_source": peak_src, "kernel": "fused_split_kernel",
+                    "peak_source": peak_src, "kernel": "splitk_kernel<FusedPolicy>",
                     "algorithmic_bytes_per_launch": cbytes,
                     "us_per_launch": ms_split * 1e3 / K,
                     "frac_of_8TBps_spec": achieved / 8000.0}
@@ -409,7 +409,7 @@ def run_ours(args):
                           f"{R * cbytes / 1e6:.0f} MB >= 3 x {l2 / 1e6:.0f} MB L2), CUDA-graph replay",
                 "partition": ("history split over ranks + NCCL all-gather of (acc,m,l) + combine"
                               if history_split else "independent sequences per rank, no collective"),
-                "num_splits": (ws.get("key") or (0, 0, 1, 0))[2],
+                "partial_slots_per_head": (ws.get("key") or (0, 0, 1, 0))[2],
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * K, "clocks": clocks, "parity_vs_oracle": parity,

@@ -95,6 +95,61 @@ __global__ void __launch_bounds__(kCombineThreads)
   }
 }
 
+// Few partials per row (large batches: 2-8 slots): one warp per (batch, head), each
+// lane a float4 slice of D, the slots walked in order.  8192 tiny CTAs of the kernel
+// above would cost more in scheduling than the merge itself.
+constexpr int kSmallWarps = 8;
+constexpr int kSmallMaxNS = 16;
+
+__global__ void __launch_bounds__(kSmallWarps * 32)
+    combine_small_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                         const float* __restrict__ l, float* __restrict__ out,
+                         float* __restrict__ out_m, float* __restrict__ out_l, int rows, int NS,
+                         int D) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kSmallWarps + warp;
+  if (row >= rows) return;
+  const float* mrow = m + (int64_t)row * NS;
+  const float* lrow = l + (int64_t)row * NS;
+  float ms[kSmallMaxNS];
+  float M = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < kSmallMaxNS; ++s) {
+    ms[s] = s < NS ? __ldg(mrow + s) : -INFINITY;
+    M = fmaxf(M, ms[s]);
+  }
+  float L = 0.f;
+#pragma unroll
+  for (int s = 0; s < kSmallMaxNS; ++s) {
+    ms[s] = (ms[s] > -INFINITY) ? ex2(ms[s] - M) : 0.f;  // weight of slot s
+    if (s < NS && ms[s] > 0.f) L = fmaf(ms[s], __ldg(lrow + s), L);
+  }
+  const float inv = (out_m == nullptr) ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
+  for (int v = lane; v < (D >> 2); v += 32) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < kSmallMaxNS; ++s) {
+      if (s < NS && ms[s] > 0.f) {  // empty slots may hold anything in acc: never read it
+        const float4 x =
+            __ldg(reinterpret_cast<const float4*>(acc + ((int64_t)row * NS + s) * D) + v);
+        a.x = fmaf(ms[s], x.x, a.x);
+        a.y = fmaf(ms[s], x.y, a.y);
+        a.z = fmaf(ms[s], x.z, a.z);
+        a.w = fmaf(ms[s], x.w, a.w);
+      }
+    }
+    a.x *= inv;
+    a.y *= inv;
+    a.z *= inv;
+    a.w *= inv;
+    reinterpret_cast<float4*>(out + (int64_t)row * D)[v] = a;
+  }
+  if (out_m != nullptr && lane == 0) {
+    out_m[row] = M;
+    out_l[row] = L;
+  }
+}
+
 }  // namespace tkv
 
 extern "C" int tkv_combine(const float* acc, const float* m, const float* l, float* out,
@@ -109,6 +164,13 @@ extern "C" int tkv_combine(const float* acc, const float* m, const float* l, flo
               "combine: acc and out must be 16-byte aligned");
   const int64_t rows = (int64_t)B * HQ;
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
+  if (NS <= kSmallMaxNS && rows >= 256) {
+    const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
+    combine_small_kernel<<<blocks, kSmallWarps * 32, 0, (cudaStream_t)stream>>>(
+        acc, m, l, out, out_m, out_l, (int)rows, NS, D);
+    TKV_CUDA(cudaGetLastError());
+    return TKV_OK;
+  }
   dim3 grid((unsigned)rows, D / kCombineSlice);
   combine_kernel<<<grid, kCombineThreads, 0, (cudaStream_t)stream>>>(acc, m, l, out, out_m, out_l,
                                                                      NS, D);

@@ -8,11 +8,14 @@
 // tile policy: how a 32-token tile is fetched and what is computed on it.
 //
 // Data movement.  A stage holds 32 tokens: K codes, V codes, and the four scale/zero
-// arrays.  Lane 0 of the warp fills it with two tiled TMA loads (tensor maps over the
-// packed code tensors viewed as [tokens, bytes-per-token], hardware 32B/64B swizzle so
-// that the later ldmatrix reads are bank-conflict free) and four 1-D bulk copies for
-// the metadata, all completing on one mbarrier per stage.  Ragged tails and caches
-// whose metadata rows are not 16-byte aligned fetch the metadata with plain loads.
+// arrays.  Lane 0 of the warp fills it with two tiled TMA loads and four 1-D bulk
+// copies for the metadata, all completing on one mbarrier per stage.  The tensor maps
+// view a packed code tensor as rows of 128 bytes (the 32 tokens of a tile are one
+// contiguous run) with the hardware 128B swizzle, or -- when sequences do not start on
+// 128-byte boundaries -- as [tokens, bytes-per-token] with the 32B/64B swizzle; either
+// way the later 8-row x 16-byte ldmatrix reads hit 8 distinct bank groups.  Ragged
+// tails and caches whose metadata rows are not 16-byte aligned fetch the metadata with
+// plain loads (tokens past the end get scale = zero = 0).
 //
 // Arithmetic.  The packed bytes are never expanded to dequantised values.  With
 // code c, group scale s and group zero z, a cache value is c*s + z, so
@@ -103,14 +106,14 @@ __device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
 }
 
 
-template <int NBITS, int D_, int GS>
+template <int NBITS, int D_, int GS, int WARPS_ = 4, int STAGES_ = 2, int MIN_CTAS_ = 4>
 struct FusedPolicy {
   using C = FusedCfg<NBITS, D_, GS>;
   static constexpr int D = D_;
   static constexpr int TOK = kTok;
-  static constexpr int WARPS = 4;
-  static constexpr int STAGES = 2;
-  static constexpr int MIN_CTAS = 4;
+  static constexpr int WARPS = WARPS_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
   static constexpr int STAGE_BYTES = C::STAGE_BYTES;
   static constexpr int P = C::P, DP = C::DP, NBLK = C::NBLK, NCH = C::NCH, NG = C::NG;
   static constexpr int NACC = C::NACC, ACC_DIMS = C::ACC_DIMS;
@@ -143,13 +146,8 @@ struct FusedPolicy {
       mbar_arrive_expect_tx(bar, 2 * kTok * DP + (bulk_meta ? 4 * C::META_BYTES : 0));
       // wide view: the tensor is [bytes/128, 128]; narrow view: [tokens, DP]
       const int c1 = p.wide ? (int)((row * DP) >> 7) : (int)row;
-      if (p.exp == 4) {  // experiment: untiled bulk copies for the codes (layout is then unswizzled)
-        bulk_load_1d(st, p.kp + row * DP, kTok * DP, bar);
-        bulk_load_1d(st + C::CODE_BYTES, p.vp + row * DP, kTok * DP, bar);
-      } else {
-        tma_load_2d(st, &maps.k, 0, c1, bar);
-        tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
-      }
+      tma_load_2d(st, &maps.k, 0, c1, bar);
+      tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
       if (bulk_meta) {
         const uint32_t mst = st + 2 * C::CODE_BYTES;
         const int64_t off = row * NG;
@@ -578,16 +576,6 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
                        : 0;
   // 128-byte-row view of the code tensors: every sequence must start on a 128-byte boundary
   p.wide = (((int64_t)S * D * nbits / 8) % 128 == 0) ? 1 : 0;
-  static const int no_wide = [] {
-    const char* e = getenv("TKV_NARROW");
-    return e ? atoi(e) : 0;
-  }();
-  if (no_wide) p.wide = 0;
-  static const int exp_mode = [] {
-    const char* e = getenv("TKV_EXP");
-    return e ? atoi(e) : 0;
-  }();
-  p.exp = exp_mode;
   SplitSched sc;
   rc = fused_plan(nbits, D, gs, &sc, B, HKV, p.hchunks, S, num_splits, split_size,
                   seq_lens != nullptr);

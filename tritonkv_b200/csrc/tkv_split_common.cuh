@@ -37,7 +37,6 @@ struct DecodeParams {
   float qk_scale;  // sm_scale * log2(e)
   int partials;    // 1: write (acc, m, l); 0: write normalised out
   int meta_aligned;  // 1: scale/zero tiles start on 16-byte boundaries (cp.async path)
-  int exp;           // development experiments (0 = normal operation)
   int wide;          // 1: code tensors are fetched as 128-byte rows (128B TMA swizzle)
 };
 

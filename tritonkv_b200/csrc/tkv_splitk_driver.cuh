@@ -249,8 +249,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
       }
       __syncwarp();
       issue_next();  // refills the stage consumed in the previous iteration
-      if (p.exp != 2 && p.exp != 4)
-        Policy::compute(acc, qs, ring_u32 + slot * STAGE_BYTES, ring + slot * STAGE_BYTES, left,
+      Policy::compute(acc, qs, ring_u32 + slot * STAGE_BYTES, ring + slot * STAGE_BYTES, left,
                         p.qk_scale, lane);
       left -= WARPS * kTok;
       ++consumed;
