@@ -252,7 +252,8 @@ def run_ours(args):
     R = max(2, harness.replicas_for(cbytes, l2))
     cbytes16 = fp16_bytes(B, HKV, S_local, D)
     R16 = max(2, harness.replicas_for(cbytes16, l2)) if not args.no_table else 0
-    reps = build_replicas(torch, Q, B, HQ, HKV, S_local, D, nbits, R, min(R16, R), args.seed + 1000 * rank, device)
+    reps = build_replicas(torch, Q, B, HQ, HKV, S_local, D, nbits, R, min(R16, R),
+                          args.seed + (0 if history_split else 1000 * rank), device)
     outs = [torch.empty(B, HQ, D, device=device) for _ in range(R)]
     ws: dict = {}
 
@@ -274,26 +275,14 @@ def run_ours(args):
 
     # ---- the step ----
     if history_split:
-        gath = {n: torch.empty(world, *s, device=device) for n, s in
-                (("acc", (B, HQ, D)), ("m", (B, HQ)), ("l", (B, HQ)))}
-        loc = {n: torch.empty(*s, device=device) for n, s in
-               (("acc", (B, HQ, D)), ("m", (B, HQ)), ("l", (B, HQ)))}
-        from tritonkv_b200.kernels import combine_splits
+        from tritonkv_b200.parallel import HistorySplitDecoder
+
+        dec = HistorySplitDecoder(B, HQ, D, device)
 
         def make_step(i):
             r = reps[i]
-            def step():
-                fused_decode_attention(r["q"], r["kq"], r["vq"], _workspace=ws, _partials_only=True,
-                                       out=outs[i])
-                combine_splits(ws["acc"], ws["maxs"], ws["sums"], out=loc["acc"], out_m=loc["m"],
-                               out_l=loc["l"])
-                for n in ("acc", "m", "l"):
-                    dist.all_gather_into_tensor(gath[n], loc[n])
-                combine_splits(gath["acc"].permute(1, 2, 0, 3).contiguous(),
-                               gath["m"].permute(1, 2, 0).contiguous(),
-                               gath["l"].permute(1, 2, 0).contiguous(), out=outs[i])
-            return step
-        launches_per_step = 2 + 3 + 3 + 1
+            return lambda: dec.step(r["q"], r["kq"], r["vq"])
+        launches_per_step = 3  # split, local merge, cross-rank merge (+ one NCCL all-gather)
     else:
         def make_step(i):
             r = reps[i]

@@ -127,6 +127,15 @@ int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const void* v, fl
 int tkv_combine(const float* acc, const float* m, const float* l, float* out, float* out_m,
                 float* out_l, int B, int HQ, int NS, int D, void* stream);
 
+/* The same merge on partials that are not laid out (rows, NS, D): slot s of row r is at
+ * acc + r*acc_row_stride + s*acc_slot_stride (floats), its m and l at
+ * r*ml_row_stride + s*ml_slot_stride.  Used for the cross-GPU history split, where the
+ * all-gathered buffer is (ranks, [acc | m | l]) -- no reference counterpart. */
+int tkv_combine_strided(const float* acc, const float* m, const float* l, float* out, float* out_m,
+                        float* out_l, int64_t rows, int NS, int D, int64_t acc_row_stride,
+                        int64_t acc_slot_stride, int64_t ml_row_stride, int64_t ml_slot_stride,
+                        void* stream);
+
 /* Resident CTAs per SM x SM count for the selected split kernel: the number of
  * programs that fill the device in one wave; the launcher's target where the
  * reference uses 4 x SM count (kernels/fused_decode_attn.py:402-416). */

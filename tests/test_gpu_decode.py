@@ -364,3 +364,36 @@ def test_no_bounded_wait_gave_up():
     fused_decode_attention(q, kq, vq)
     torch.cuda.synchronize()
     assert _cabi.device_status() == 0
+
+
+# ------------------------------------------------------------------ history split over ranks
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_history_split_merge_emulated_on_one_gpu(world):
+    """The cross-GPU history split with all ranks' work done in turn on one GPU: every
+    "rank" reduces its token range to one unnormalised partial in the wire layout, the
+    gathered buffer is merged by the strided combine kernel, and the result equals the
+    oracle on the whole history (Llama-3-70B head layout, 2-bit, shortened context)."""
+    from tritonkv_b200 import parallel as P
+    from tritonkv_b200.kernels import combine_splits as combine
+
+    B, HQ, HKV, S, D = 1, 64, 8, 5000, 128
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=95)
+    kq, vq = Q.quantize_kv(k, v, 2, 32)
+    n = P.wire_floats(B, HQ, D)
+    gathered = torch.empty(world, n, device=DEV)
+    for r in range(world):
+        lo, hi = P.history_shard(S, world, r)
+        if hi <= lo:
+            P.empty_partial_(gathered[r], B, HQ, D)
+            continue
+        sl = lambda t: Q.QuantizedTensor(t.packed[:, :, lo:hi].contiguous(),
+                                         t.scale[:, :, lo:hi].contiguous(),
+                                         t.zero[:, :, lo:hi].contiguous(), 2, 32, D)
+        ws = {}
+        fused_decode_attention(q, sl(kq), sl(vq), _workspace=ws, _partials_only=True)
+        acc, m, l = P.wire_views(gathered[r], B, HQ, D)
+        combine(ws["acc"], ws["maxs"], ws["sums"], out=acc, out_m=m, out_l=l)
+    got = P.merge_gathered(gathered, B, HQ, D)
+    assert_close(got, oracle_attention(q, kq, vq), f"history split over {world} ranks")

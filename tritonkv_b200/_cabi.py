@@ -50,6 +50,9 @@ SIGNATURES = {
                                 c_int, c_void_p, c_int, c_void_p]),
     "tkv_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_void_p]),
+    "tkv_combine_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
+                                    c_void_p]),
     "tkv_wave_programs": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
     "tkv_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, POINTER(c_int), POINTER(c_int)]),

@@ -20,7 +20,8 @@ constexpr int kCombineSlice = 32;  // head dims per CTA
 __global__ void __launch_bounds__(kCombineThreads)
     combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
                    const float* __restrict__ l, float* __restrict__ out, float* __restrict__ out_m,
-                   float* __restrict__ out_l, int NS, int D) {
+                   float* __restrict__ out_l, int NS, int D, int64_t a_row, int64_t a_slot,
+                   int64_t ml_row, int64_t ml_slot) {
   __shared__ float red_m[8];
   __shared__ float4 red_a[8][8];
   __shared__ float red_l[8];
@@ -28,12 +29,12 @@ __global__ void __launch_bounds__(kCombineThreads)
   const int row = blockIdx.x;            // b*HQ + h
   const int d0 = blockIdx.y * kCombineSlice;
   const int sg = tid >> 3, dl = tid & 7; // split group (0..31), float4 index inside the slice
-  const float* mrow = m + (int64_t)row * NS;
-  const float* lrow = l + (int64_t)row * NS;
-  const float* arow = acc + (int64_t)row * NS * D + d0 + dl * 4;
+  const float* mrow = m + (int64_t)row * ml_row;
+  const float* lrow = l + (int64_t)row * ml_row;
+  const float* arow = acc + (int64_t)row * a_row + d0 + dl * 4;
 
   float mloc = -INFINITY;
-  for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s));
+  for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s * ml_slot));
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
   if (lane == 0) red_m[warp] = mloc;
@@ -46,15 +47,15 @@ __global__ void __launch_bounds__(kCombineThreads)
   float L = 0.f;
 #pragma unroll 4
   for (int s = sg; s < NS; s += 32) {
-    const float ms = __ldg(mrow + s);
+    const float ms = __ldg(mrow + s * ml_slot);
     if (ms > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never read it
       const float w = ex2(ms - M);
-      const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * D));
+      const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
       a.x = fmaf(w, x.x, a.x);
       a.y = fmaf(w, x.y, a.y);
       a.z = fmaf(w, x.z, a.z);
       a.w = fmaf(w, x.w, a.w);
-      L = fmaf(w, __ldg(lrow + s), L);
+      L = fmaf(w, __ldg(lrow + s * ml_slot), L);
     }
   }
   // the 4 split groups of a warp (lanes dl, dl+8, dl+16, dl+24)
@@ -105,24 +106,24 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
     combine_small_kernel(const float* __restrict__ acc, const float* __restrict__ m,
                          const float* __restrict__ l, float* __restrict__ out,
                          float* __restrict__ out_m, float* __restrict__ out_l, int rows, int NS,
-                         int D) {
+                         int D, int64_t a_row, int64_t a_slot, int64_t ml_row, int64_t ml_slot) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kSmallWarps + warp;
   if (row >= rows) return;
-  const float* mrow = m + (int64_t)row * NS;
-  const float* lrow = l + (int64_t)row * NS;
+  const float* mrow = m + (int64_t)row * ml_row;
+  const float* lrow = l + (int64_t)row * ml_row;
   float ms[kSmallMaxNS];
   float M = -INFINITY;
 #pragma unroll
   for (int s = 0; s < kSmallMaxNS; ++s) {
-    ms[s] = s < NS ? __ldg(mrow + s) : -INFINITY;
+    ms[s] = s < NS ? __ldg(mrow + s * ml_slot) : -INFINITY;
     M = fmaxf(M, ms[s]);
   }
   float L = 0.f;
 #pragma unroll
   for (int s = 0; s < kSmallMaxNS; ++s) {
     ms[s] = (ms[s] > -INFINITY) ? ex2(ms[s] - M) : 0.f;  // weight of slot s
-    if (s < NS && ms[s] > 0.f) L = fmaf(ms[s], __ldg(lrow + s), L);
+    if (s < NS && ms[s] > 0.f) L = fmaf(ms[s], __ldg(lrow + s * ml_slot), L);
   }
   const float inv = (out_m == nullptr) ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
   for (int v = lane; v < (D >> 2); v += 32) {
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
     for (int s = 0; s < kSmallMaxNS; ++s) {
       if (s < NS && ms[s] > 0.f) {  // empty slots may hold anything in acc: never read it
         const float4 x =
-            __ldg(reinterpret_cast<const float4*>(acc + ((int64_t)row * NS + s) * D) + v);
+            __ldg(reinterpret_cast<const float4*>(acc + (int64_t)row * a_row + s * a_slot) + v);
         a.x = fmaf(ms[s], x.x, a.x);
         a.y = fmaf(ms[s], x.y, a.y);
         a.z = fmaf(ms[s], x.z, a.z);
@@ -152,28 +153,41 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
 
 }  // namespace tkv
 
-extern "C" int tkv_combine(const float* acc, const float* m, const float* l, float* out,
-                           float* out_m, float* out_l, int B, int HQ, int NS, int D, void* stream) {
+extern "C" int tkv_combine_strided(const float* acc, const float* m, const float* l, float* out,
+                                   float* out_m, float* out_l, int64_t rows, int NS, int D,
+                                   int64_t acc_row_stride, int64_t acc_slot_stride,
+                                   int64_t ml_row_stride, int64_t ml_slot_stride, void* stream) {
   using namespace tkv;
   TKV_REQUIRE(acc && m && l && out, TKV_ERR_INVALID, "combine: null pointer");
   TKV_REQUIRE((out_m == nullptr) == (out_l == nullptr), TKV_ERR_INVALID,
               "combine: out_m and out_l must be given together");
-  TKV_REQUIRE(B > 0 && HQ > 0 && NS > 0 && D > 0 && D % kCombineSlice == 0, TKV_ERR_INVALID,
-              "combine: bad sizes B=%d HQ=%d NS=%d D=%d (D must be a multiple of 32)", B, HQ, NS, D);
-  TKV_REQUIRE(aligned16(acc) && aligned16(out), TKV_ERR_ALIGN,
-              "combine: acc and out must be 16-byte aligned");
-  const int64_t rows = (int64_t)B * HQ;
+  TKV_REQUIRE(rows > 0 && NS > 0 && D > 0 && D % kCombineSlice == 0, TKV_ERR_INVALID,
+              "combine: bad sizes rows=%lld NS=%d D=%d (D must be a multiple of 32)",
+              (long long)rows, NS, D);
+  TKV_REQUIRE(aligned16(acc) && aligned16(out) && acc_row_stride % 4 == 0 && acc_slot_stride % 4 == 0,
+              TKV_ERR_ALIGN, "combine: acc and out must be 16-byte aligned, acc strides multiples of 4");
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
   if (NS <= kSmallMaxNS && rows >= 256) {
     const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
     combine_small_kernel<<<blocks, kSmallWarps * 32, 0, (cudaStream_t)stream>>>(
-        acc, m, l, out, out_m, out_l, (int)rows, NS, D);
+        acc, m, l, out, out_m, out_l, (int)rows, NS, D, acc_row_stride, acc_slot_stride,
+        ml_row_stride, ml_slot_stride);
     TKV_CUDA(cudaGetLastError());
     return TKV_OK;
   }
   dim3 grid((unsigned)rows, D / kCombineSlice);
-  combine_kernel<<<grid, kCombineThreads, 0, (cudaStream_t)stream>>>(acc, m, l, out, out_m, out_l,
-                                                                     NS, D);
+  combine_kernel<<<grid, kCombineThreads, 0, (cudaStream_t)stream>>>(
+      acc, m, l, out, out_m, out_l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
+      ml_slot_stride);
   TKV_CUDA(cudaGetLastError());
   return TKV_OK;
+}
+
+extern "C" int tkv_combine(const float* acc, const float* m, const float* l, float* out,
+                           float* out_m, float* out_l, int B, int HQ, int NS, int D, void* stream) {
+  using namespace tkv;
+  TKV_REQUIRE(B > 0 && HQ > 0 && NS > 0 && D > 0, TKV_ERR_INVALID,
+              "combine: bad sizes B=%d HQ=%d NS=%d D=%d", B, HQ, NS, D);
+  return tkv_combine_strided(acc, m, l, out, out_m, out_l, (int64_t)B * HQ, NS, D,
+                             (int64_t)NS * D, D, NS, 1, stream);
 }

@@ -106,7 +106,7 @@ __device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
 }
 
 
-template <int NBITS, int D_, int GS, int WARPS_ = 4, int STAGES_ = 2, int MIN_CTAS_ = 4>
+template <int NBITS, int D_, int GS, int WARPS_ = 4, int STAGES_ = 3, int MIN_CTAS_ = 3>
 struct FusedPolicy {
   using C = FusedCfg<NBITS, D_, GS>;
   static constexpr int D = D_;
