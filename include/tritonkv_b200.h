@@ -141,6 +141,23 @@ int tkv_combine_strided(const float* acc, const float* m, const float* l, float*
  * reference uses 4 x SM count (kernels/fused_decode_attn.py:402-416). */
 int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* programs);
 
+/* tkv_fused_decode + tkv_combine for callers that cannot provide the (acc, m, l) partial
+ * buffers because they cannot allocate device memory at the point of the call: code
+ * running under a frozen memory pool, inside a region where cudaMalloc is forbidden, or
+ * as a plugin of a host that owns all device memory.  It has no counterpart in the
+ * reference (whose launcher allocates its workspace with torch.empty).  The partials go
+ * to an 8 MiB array inside the library image (held by every GPU that loads the library
+ * until exit); the call itself allocates nothing.  Limit: B*HQ*nslots*(D+2) floats must
+ * fit 8 MiB (nslots from tkv_decode_plan with num_splits = 1, split_size = S rounded up
+ * to 16); larger problems get TKV_ERR_UNSUPPORTED.  The first call on a device looks up
+ * the array's device address (one-time set-up, make it before any stream capture).  All
+ * calls on a device share the array: calls that overlap on the GPU (different streams)
+ * race on it -- serialise them.  Uniform history length only (no seq_lens). */
+int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t* k_packed,
+                            const void* k_scale, const void* k_zero, const uint8_t* v_packed,
+                            const void* v_scale, const void* v_zero, float* out, int B, int HQ,
+                            int HKV, int S, int D, int nbits, int gs, float sm_scale, void* stream);
+
 /* Device-side status word of the current device (synchronises with it): 0 = ok,
  * 1 = a bounded wait on a copy barrier inside a decode kernel gave up (the kernel then
  * returned early and its output is invalid).  No reference counterpart: the Triton

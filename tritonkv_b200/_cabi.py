@@ -57,6 +57,9 @@ SIGNATURES = {
     "tkv_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, POINTER(c_int), POINTER(c_int)]),
     "tkv_device_status": (c_int, [POINTER(c_int)]),
+    "tkv_fused_decode_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_float, c_void_p]),
 }
 
 _lib = None

@@ -29,6 +29,7 @@ SOURCES = [
     "tkv_combine.cu",
     "tkv_decode_fused.cu",
     "tkv_decode_fp16.cu",
+    "tkv_decode_static.cu",
 ]
 
 NVCC_FLAGS = [
