@@ -4,8 +4,8 @@
 // Scheduling, the per-warp copy rings and the epilogue are the shared driver of
 // tkv_splitk_driver.cuh -- identical split, online softmax, GQA grouping and partial
 // format as the packed-cache kernel; this file is the tile policy: K and V tiles are
-// plain f16 rows, fetched by tiled TMA loads (128-byte column halves, hardware 128B
-// swizzle) and read with ldmatrix (K as the A operand of S^T = K Q^T, V with .trans as
+// plain f16 rows, fetched with 16-byte cp.async copies into a 128B-swizzled layout
+// (completion posted on the stage's mbarrier) and read with ldmatrix (K as the A operand of S^T = K Q^T, V with .trans as
 // the A operand of O^T = V^T P^T).
 #include "tkv_splitk_driver.cuh"
 
@@ -20,6 +20,7 @@ struct Fp16Policy {
   static constexpr int WARPS = 4;
   static constexpr int STAGES = (D_ >= 128) ? 3 : 4;
   static constexpr int MIN_CTAS = 2;
+  static constexpr int BAR_COUNT = 32;  // one arrival per lane
   static constexpr int ROW = 2 * D;            // bytes per token row
   static constexpr int NH = ROW / 128;         // 128-byte column halves per row
   static constexpr int NCH = D / 16;           // 16-dim MMA chunks
@@ -32,7 +33,7 @@ struct Fp16Policy {
   static_assert(ROW % 128 == 0, "head_dim must be a multiple of 64");
 
   struct Maps {
-    CUtensorMap k, v;
+    int unused;
   };
   struct Query {
     uint32_t qf[NCH][2];
@@ -44,34 +45,48 @@ struct Fp16Policy {
 
   __device__ static void report_timeout() { atomicExch(&g_fp16_status, 1); }
 
+  // Byte offset of the 16-byte chunk `c16` (0 .. ROW/16) of token row r inside a tile.
+  __device__ static __forceinline__ uint32_t chunk_off(int r, int c16) {
+    const int h = c16 >> 3, c = c16 & 7;
+    return h * SUB_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+  }
+
+
+  // Fill one stage with the 16 tokens starting at global row `row`: 16-byte cp.async per
+  // lane into the 128B-swizzled layout (rows past the unit end are zero-filled), then one
+  // arrival per lane on the stage barrier that fires when the lane's copies have landed.
   __device__ static __forceinline__ void issue(const DecodeParams& p, const Maps& maps, int64_t row,
                                                int nvalid, uint32_t st, uint8_t* st_ptr,
                                                uint32_t bar, int lane) {
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar, PAYLOAD);
+    constexpr int NCC = TOK * (ROW / 16);  // 16-byte chunks per tile
+    const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(p.k) + row * ROW;
+    const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.v) + row * ROW;
 #pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        tma_load_2d(st + h * SUB_BYTES, &maps.k, h * 128, (int)row, bar);
-        tma_load_2d(st + TILE_BYTES + h * SUB_BYTES, &maps.v, h * 128, (int)row, bar);
-      }
+    for (int i0 = 0; i0 < NCC; i0 += 32) {
+      const int i = i0 + lane;
+      const int r = i / (ROW / 16), c16 = i % (ROW / 16);
+      const uint32_t dst = chunk_off(r, c16);
+      const bool ok = r < nvalid;
+      cp_async16(st + dst, ok ? ksrc + i * 16 : reinterpret_cast<const uint8_t*>(p.k), ok ? 16 : 0);
+      cp_async16(st + TILE_BYTES + dst, ok ? vsrc + i * 16 : reinterpret_cast<const uint8_t*>(p.v),
+                 ok ? 16 : 0);
     }
+    cp_async_mbar_arrive_noinc(bar);
   }
 
   // query fragments: B operand, k-slots (2t,2t+1) <-> dims 16c+2t, 16c+2t+1 and
   // (2t+8, 2t+9) <-> dims 16c+8+2t, 16c+9+2t, column g = head g.
-  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p, int b, int hkv,
-                                                    int hc, int lane) {
+  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p,
+                                                    const uint8_t* qsm, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    const int head = hc * kHeadsPerCta + g;
-    const bool head_ok = head < p.group;
-    const int64_t qoff = ((int64_t)b * p.HQ + (int64_t)hkv * p.group + head) * D;
+    const uint8_t* qrow = qsm + g * D * (p.q_dtype == TKV_DTYPE_F32 ? 4 : 2);
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
       __half x[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int d = 16 * ch + 2 * t + (i & 1) + (i >> 1) * 8;
-        x[i] = head_ok ? load_q_half(p.q, p.q_dtype, qoff + d) : __float2half(0.f);
+        x[i] = load_q_half(qrow, p.q_dtype, d);
       }
       qq.qf[ch][0] = pack_half2(x[0], x[1]);
       qq.qf[ch][1] = pack_half2(x[2], x[3]);
@@ -87,40 +102,26 @@ struct Fp16Policy {
       for (int i = 0; i < 4; ++i) ac.acc[ch][i] = 0.f;
   }
 
-  // Byte offset of the 16-byte chunk `c16` (0 .. ROW/16) of token row r inside a tile.
-  __device__ static __forceinline__ uint32_t chunk_off(int r, int c16) {
-    const int h = c16 >> 3, c = c16 & 7;
-    return h * SUB_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
-  }
+  struct Scores {
+    float s[4];  // (token g, head 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+  };
 
-  __device__ static __forceinline__ void compute(Accum& ac, const Query& qq, uint32_t st,
-                                                 uint8_t* st_ptr, int left, float qk_scale,
-                                                 int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    const uint32_t kt = st, vt = st + TILE_BYTES;
-    if (left < TOK) {
-      // rows past the end of the unit hold other tokens (or nothing): zero V there so
-      // that p = 0 meets a finite value
-      for (int i = lane; i < (TOK - left) * (ROW / 16); i += 32) {
-        const int r = left + i / (ROW / 16), c16 = i % (ROW / 16);
-        *reinterpret_cast<uint4*>(st_ptr + TILE_BYTES + chunk_off(r, c16)) = make_uint4(0, 0, 0, 0);
-      }
-      __syncwarp();
-    }
+  // Scores of one 16-token tile (scaled, tokens past the unit end set to -inf).
+  __device__ static __forceinline__ void scores(Scores& out, const Query& qq, uint32_t st,
+                                                const uint8_t* st_ptr, int left, float qk_scale,
+                                                int lane) {
+    const int g = lane >> 2;
     // K (A operand): matrices (tok 0-7, chunk 2c), (tok 8-15, chunk 2c), (tok 0-7, chunk 2c+1),
     // (tok 8-15, chunk 2c+1)
     const int k_r = (lane & 7) + ((lane >> 3) & 1) * 8;
     const int k_c = lane >> 4;
-    // V (A operand of O^T, via .trans): matrices (tok 0-7, chunk 2i), (tok 0-7, chunk 2i+1),
-    // (tok 8-15, chunk 2i), (tok 8-15, chunk 2i+1)
-    const int v_r = (lane & 7) + (lane >> 4) * 8;
-    const int v_c = (lane >> 3) & 1;
-
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    float (&sc)[4] = out.s;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i] = 0.f;
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
       uint32_t r[4];
-      ldmatrix_x4(r, kt + chunk_off(k_r, 2 * ch + k_c));
+      ldmatrix_x4(r, st + chunk_off(k_r, 2 * ch + k_c));
       mma16816(sc, r[0], r[1], r[2], r[3], qq.qf[ch][0], qq.qf[ch][1]);
     }
 #pragma unroll
@@ -129,6 +130,17 @@ struct Fp16Policy {
       if (g >= left) sc[0] = sc[1] = -INFINITY;
       if (g + 8 >= left) sc[2] = sc[3] = -INFINITY;
     }
+  }
+
+  // Online softmax update and O^T += V^T P^T for the tile whose scores are `in`.
+  __device__ static __forceinline__ void update(Accum& ac, const Query& qq, Scores& in,
+                                                uint32_t st, uint8_t* st_ptr, int left, int lane) {
+    const uint32_t vt = st + TILE_BYTES;
+    float (&sc)[4] = in.s;
+    // V (A operand of O^T, via .trans): matrices (tok 0-7, chunk 2i), (tok 0-7, chunk 2i+1),
+    // (tok 8-15, chunk 2i), (tok 8-15, chunk 2i+1)
+    const int v_r = (lane & 7) + (lane >> 4) * 8;
+    const int v_c = (lane >> 3) & 1;
 
     // online softmax with a lazily raised reference exponent
     {
@@ -230,10 +242,8 @@ static int fp16_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStre
   using P = Fp16Policy<D>;
   typename P::Maps maps;
   const int64_t rows = (int64_t)p.B * p.HKV * p.S;
-  int rc = make_row_map(&maps.k, p.k, rows, P::ROW, 128, P::TOK);
-  if (rc != TKV_OK) return rc;
-  rc = make_row_map(&maps.v, p.v, rows, P::ROW, 128, P::TOK);
-  if (rc != TKV_OK) return rc;
+  (void)rows;  // the control kernel addresses K and V directly; no tensor maps
+  maps.unused = 0;
   return SplitLaunch<P>::launch(maps, p, sc, stream);
 }
 

@@ -8,14 +8,16 @@
 // tile policy: how a 32-token tile is fetched and what is computed on it.
 //
 // Data movement.  A stage holds 32 tokens: K codes, V codes, and the four scale/zero
-// arrays.  Lane 0 of the warp fills it with two tiled TMA loads and four 1-D bulk
-// copies for the metadata, all completing on one mbarrier per stage.  The tensor maps
+// arrays.  Lane 0 of the warp fetches the codes with two tiled TMA loads; every lane
+// fetches a share of the metadata with 16-byte cp.async copies and posts one arrival
+// that fires when they land; all of it completes on one mbarrier per stage.  The tensor maps
 // view a packed code tensor as rows of 128 bytes (the 32 tokens of a tile are one
 // contiguous run) with the hardware 128B swizzle, or -- when sequences do not start on
 // 128-byte boundaries -- as [tokens, bytes-per-token] with the 32B/64B swizzle; either
 // way the later 8-row x 16-byte ldmatrix reads hit 8 distinct bank groups.  Ragged
 // tails and caches whose metadata rows are not 16-byte aligned fetch the metadata with
-// plain loads (tokens past the end get scale = zero = 0).
+// plain loads (tokens past the end get scale = zero = 0).  The query rows of a segment
+// are staged in shared memory by the driver, one segment ahead.
 //
 // Arithmetic.  The packed bytes are never expanded to dequantised values.  With
 // code c, group scale s and group zero z, a cache value is c*s + z, so
@@ -115,6 +117,8 @@ struct FusedPolicy {
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
   static constexpr int STAGE_BYTES = C::STAGE_BYTES;
+  // arrivals per stage: lane 0's expect_tx for the code tiles + one per lane for the metadata
+  static constexpr int BAR_COUNT = 33;
   static constexpr int P = C::P, DP = C::DP, NBLK = C::NBLK, NCH = C::NCH, NG = C::NG;
   static constexpr int NACC = C::NACC, ACC_DIMS = C::ACC_DIMS;
 
@@ -141,23 +145,31 @@ struct FusedPolicy {
   __device__ static __forceinline__ void issue(const DecodeParams& p, const Maps& maps, int64_t row,
                                                int nvalid, uint32_t st, uint8_t* st_ptr,
                                                uint32_t bar, int lane) {
-    const bool bulk_meta = p.meta_aligned && nvalid == kTok;
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar, 2 * kTok * DP + (bulk_meta ? 4 * C::META_BYTES : 0));
+      mbar_arrive_expect_tx(bar, 2 * kTok * DP);
       // wide view: the tensor is [bytes/128, 128]; narrow view: [tokens, DP]
       const int c1 = p.wide ? (int)((row * DP) >> 7) : (int)row;
       tma_load_2d(st, &maps.k, 0, c1, bar);
       tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
-      if (bulk_meta) {
-        const uint32_t mst = st + 2 * C::CODE_BYTES;
-        const int64_t off = row * NG;
-        bulk_load_1d(mst, p.ks + off, C::META_BYTES, bar);
-        bulk_load_1d(mst + C::META_BYTES, p.kz + off, C::META_BYTES, bar);
-        bulk_load_1d(mst + 2 * C::META_BYTES, p.vs + off, C::META_BYTES, bar);
-        bulk_load_1d(mst + 3 * C::META_BYTES, p.vz + off, C::META_BYTES, bar);
-      }
     }
-    if (!bulk_meta) {
+    // Scale/zero: 16-byte cp.async per lane (a bulk-copy instruction costs the issuing warp
+    // ~100+ cycles each, four of them per tile were a third of the loop time); every lane
+    // then posts one arrival on the stage barrier that fires when its copies have landed.
+    const uint32_t mst = st + 2 * C::CODE_BYTES;
+    if (p.meta_aligned && nvalid == kTok) {
+      constexpr int CPA = C::META_BYTES / 16;  // 16-byte chunks per metadata array
+      const int64_t off = row * NG;            // halves
+#pragma unroll
+      for (int i0 = 0; i0 < 4 * CPA; i0 += 32) {
+        const int i = i0 + lane;
+        if (4 * CPA >= 32 || i < 4 * CPA) {
+          const int arr = i / CPA, c = i - arr * CPA;
+          const __half* base = arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz;
+          cp_async16(mst + i * 16, reinterpret_cast<const uint8_t*>(base + off) + c * 16, 16);
+        }
+      }
+      cp_async_mbar_arrive_noinc(bar);
+    } else {
       // ragged tail or unaligned rows: plain loads; tokens past the end get scale = zero = 0
       __half* dstm = reinterpret_cast<__half*>(st_ptr + 2 * C::CODE_BYTES);
       const int64_t off = row * NG;
@@ -169,11 +181,13 @@ struct FusedPolicy {
         dstm[2 * kTok * NG + i] = ok ? p.vs[off + i] : zero;
         dstm[3 * kTok * NG + i] = ok ? p.vz[off + i] : zero;
       }
+      mbar_arrive(bar);
     }
   }
 
-  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p, int b, int hkv,
-                                                    int hc, int lane) {
+  // `qsm`: the segment's 8 query rows (raw dtype, zero rows for heads past the group)
+  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p,
+                                                    const uint8_t* qsm, int lane) {
     const int g = lane >> 2, t = lane & 3;
     {
       // ldmatrix addressing: lane l supplies the row address of matrix l/8, row l%8;
@@ -196,9 +210,7 @@ struct FusedPolicy {
           qq.off[mt][pr] = Ls << 4;
         }
     }
-    const int head = hc * kHeadsPerCta + g;
-    const bool head_ok = head < p.group;
-    const int64_t qoff = ((int64_t)b * p.HQ + (int64_t)hkv * p.group + head) * D;
+    const uint8_t* qrow = qsm + g * D * (p.q_dtype == TKV_DTYPE_F32 ? 4 : 2);
     float gsum[NG];
 #pragma unroll
     for (int i = 0; i < NG; ++i) gsum[i] = 0.f;
@@ -206,16 +218,11 @@ struct FusedPolicy {
     for (int ch = 0; ch < NCH; ++ch) {
       __half x[4];
       if (p.q_dtype == TKV_DTYPE_F16) {
-        uint2 v = make_uint2(0u, 0u);
-        if (head_ok)
-          v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.q) + qoff +
-                                                   16 * ch + 4 * t));
-        *reinterpret_cast<uint2*>(x) = v;
+        *reinterpret_cast<uint2*>(x) =
+            *reinterpret_cast<const uint2*>(qrow + (16 * ch + 4 * t) * 2);
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          x[i] = head_ok ? load_q_half(p.q, p.q_dtype, qoff + 16 * ch + 4 * t + i)
-                         : __float2half(0.f);
+        for (int i = 0; i < 4; ++i) x[i] = load_q_half(qrow, p.q_dtype, 16 * ch + 4 * t + i);
       }
       qq.qf[ch][0] = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
       qq.qf[ch][1] = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
@@ -252,20 +259,22 @@ struct FusedPolicy {
     for (int i = 0; i < 4; ++i) ac.zacc[i] = 0.f;
   }
 
-  // One 32-token tile in stage `st`; `left` = tokens from the tile start to the unit end.
-  __device__ static __forceinline__ void compute(Accum& ac, const Query& qq, uint32_t st,
-                                                 const uint8_t* st_ptr, int left, float qk_scale,
-                                                 int lane) {
+  struct Scores {
+    float s[2][4];  // [16-token half][(token g, head 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)]
+  };
+
+  // Scores of one 32-token tile in stage `st` (scaled by qk_scale, tokens past the unit
+  // end set to -inf); `left` = tokens from the tile start to the unit end.
+  __device__ static __forceinline__ void scores(Scores& out, const Query& qq, uint32_t st,
+                                                const uint8_t* st_ptr, int left, float qk_scale,
+                                                int lane) {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t kc = st;
-    const uint32_t vc = kc + C::CODE_BYTES;
     const __half* ks_s = reinterpret_cast<const __half*>(st_ptr + 2 * C::CODE_BYTES);
     const __half* kz_s = ks_s + kTok * NG;
-    const __half* vs_s = kz_s + kTok * NG;
-    const __half* vz_s = vs_s + kTok * NG;
 
   // ================= scores for the two 16-token halves ============================
-  float sc[2][4];
+  float (&sc)[2][4] = out.s;
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt) {
     float c[NACC][4];
@@ -341,7 +350,16 @@ struct FusedPolicy {
       if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
     }
   }
+  }
 
+  // Online softmax update and O^T += V^T P^T for the tile whose scores are `in`.
+  __device__ static __forceinline__ void update(Accum& ac, const Query& qq, Scores& in,
+                                                uint32_t st, uint8_t* st_ptr, int left, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t vc = st + C::CODE_BYTES;
+    const __half* vs_s = reinterpret_cast<const __half*>(st_ptr + 2 * C::CODE_BYTES) + 2 * kTok * NG;
+    const __half* vz_s = vs_s + kTok * NG;
+    float (&sc)[2][4] = in.s;
   // ================= online softmax with a lazily raised reference exponent ========
   {
     float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));

@@ -139,6 +139,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   constexpr int kTok = Policy::TOK;
   constexpr int STAGE_BYTES = Policy::STAGE_BYTES;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte alignment");
+  static_assert(STAGES >= 3, "two tiles are resident at once (scores of i+1, update of i)");
   static_assert(STAGE_BYTES >= kHeadsPerCta * D * 4, "a stage must hold one warp's partial");
 
   extern __shared__ uint8_t smem_raw[];
@@ -155,12 +156,38 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   const uint32_t ring_u32 = smem_u32(ring);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)WARPS * STAGES * STAGE_BYTES);
   const uint32_t bar_u32 = smem_u32(bars + warp * STAGES);
+  // query rows of a segment (8 heads x D, raw dtype) are staged in shared memory and
+  // prefetched one segment ahead: a global load issued when it is needed waits behind the
+  // whole copy stream (measured ~3 us under load), which the prefetch hides.
+  constexpr int QB = kHeadsPerCta * D * 4;
+  uint64_t* qbars = bars + WARPS * STAGES;
+  const uint32_t qbar_u32 = smem_u32(qbars);
+  uint8_t* qbuf = reinterpret_cast<uint8_t*>(qbars + 2);
+  const uint32_t qbuf_u32 = smem_u32(qbuf);
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + 8 * s, 1);
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + 8 * s, Policy::BAR_COUNT);
+    if (warp == 0) {
+      mbar_init(qbar_u32, WARPS * 32);
+      mbar_init(qbar_u32 + 8, WARPS * 32);
+    }
     fence_barrier_init();
   }
-  __syncwarp();
+  __syncthreads();
+  const int q_esz = p.q_dtype == TKV_DTYPE_F32 ? 4 : 2;
+  auto prefetch_q = [&](int slot, int b, int hkv, int hc) {
+    const int row_bytes = D * q_esz, cpr = row_bytes >> 4;
+    for (int i = threadIdx.x; i < kHeadsPerCta * cpr; i += WARPS * 32) {
+      const int h = i / cpr, c = i - h * cpr;
+      const int hg = hc * kHeadsPerCta + h;
+      const bool ok = hg < p.group;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                           (((int64_t)b * p.HQ + (int64_t)hkv * p.group + hg) * D) * q_esz + c * 16;
+      cp_async16(qbuf_u32 + slot * QB + h * row_bytes + c * 16,
+                 ok ? src : reinterpret_cast<const uint8_t*>(p.q), ok ? 16 : 0);
+    }
+    cp_async_mbar_arrive_noinc(qbar_u32 + 8 * slot);
+  };
 
   // ---- this CTA's tile range ----
   int g0, g1;
@@ -229,6 +256,12 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   };
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue_next();
+  prefetch_q(0, seg.b, seg.hkv, seg.hc);
+  if (sc.persistent && seg.g_end < g1) {
+    const Segment s1 = segment_at<kTok>(p, sc, seg.g_end, g1, cta);
+    prefetch_q(1, s1.b, s1.hkv, s1.hc);
+  }
+  int seg_k = 0;  // index of the current segment within this CTA
 
   int consumed = 0;
   bool timed_out = false;
@@ -237,22 +270,44 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
 
   for (int g = g0;;) {
     // ---- one segment ----
-    Policy::load_query(qs, p, seg.b, seg.hkv, seg.hc, lane);
+    if (!mbar_wait_bounded(qbar_u32 + 8 * (seg_k & 1), (seg_k >> 1) & 1)) timed_out = true;
+    Policy::load_query(qs, p, qbuf + (seg_k & 1) * QB, lane);
     Policy::reset(acc);
     const int my_tiles = seg.ntiles > warp ? (seg.ntiles - warp + WARPS - 1) / WARPS : 0;
     int left = seg.hi - (seg.lo_tok + warp * kTok);
-    for (int i = 0; i < my_tiles && !timed_out; ++i) {
-      const int slot = consumed % STAGES;
-      if (!mbar_wait_bounded(bar_u32 + 8 * slot, (consumed / STAGES) & 1)) {
-        timed_out = true;
-        break;
-      }
+    // Software pipeline: the scores of tile i+1 are computed in the same straight-line
+    // block as the softmax/output update of tile i, so the two independent dependency
+    // chains interleave in the instruction stream.
+    auto stage_u32 = [&](int k) { return ring_u32 + (k % STAGES) * STAGE_BYTES; };
+    auto stage_ptr = [&](int k) { return ring + (k % STAGES) * STAGE_BYTES; };
+    auto wait_tile = [&](int k) {
+      if (!mbar_wait_bounded(bar_u32 + 8 * (k % STAGES), (k / STAGES) & 1)) timed_out = true;
+    };
+    if (my_tiles > 0 && !timed_out) {
+      typename Policy::Scores sc_cur;
+      wait_tile(consumed);
       __syncwarp();
-      issue_next();  // refills the stage consumed in the previous iteration
-      Policy::compute(acc, qs, ring_u32 + slot * STAGE_BYTES, ring + slot * STAGE_BYTES, left,
-                        p.qk_scale, lane);
-      left -= WARPS * kTok;
-      ++consumed;
+      if (!timed_out)
+        Policy::scores(sc_cur, qs, stage_u32(consumed), stage_ptr(consumed), left, p.qk_scale, lane);
+      for (int i = 0; i + 1 < my_tiles && !timed_out; ++i) {
+        wait_tile(consumed + 1);
+        if (timed_out) break;
+        __syncwarp();
+        issue_next();  // refills the stage whose tile was finished in the previous iteration
+        typename Policy::Scores sc_next;
+        Policy::scores(sc_next, qs, stage_u32(consumed + 1), stage_ptr(consumed + 1),
+                       left - WARPS * kTok, p.qk_scale, lane);
+        Policy::update(acc, qs, sc_cur, stage_u32(consumed), stage_ptr(consumed), left, lane);
+        sc_cur = sc_next;
+        left -= WARPS * kTok;
+        ++consumed;
+      }
+      if (!timed_out) {
+        __syncwarp();
+        issue_next();
+        Policy::update(acc, qs, sc_cur, stage_u32(consumed), stage_ptr(consumed), left, lane);
+        ++consumed;
+      }
     }
 
     // ---- segment epilogue: merge the warps, store the partial ----
@@ -323,6 +378,11 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     g = seg.g_end;
     if (g >= g1 || timed_out) break;
     seg = segment_at<kTok>(p, sc, g, g1, cta);
+    if (seg.g_end < g1) {  // the query slot just released takes the segment after the next
+      const Segment s2 = segment_at<kTok>(p, sc, seg.g_end, g1, cta);
+      prefetch_q(seg_k & 1, s2.b, s2.hkv, s2.hc);
+    }
+    ++seg_k;
   }
   if (timed_out && lane == 0) Policy::report_timeout();
 }
@@ -374,7 +434,8 @@ template <class Policy>
 struct SplitLaunch {
   static int smem_bytes() {
     return Policy::WARPS * Policy::STAGES * Policy::STAGE_BYTES + Policy::WARPS * Policy::STAGES * 8 +
-           1024;  // slack for the 1024-byte alignment of the ring
+           16 + 2 * kHeadsPerCta * Policy::D * 4 +  // query barriers and the two query slots
+           1024;                                    // slack for the 1024-byte alignment of the ring
   }
   static const void* fn() { return reinterpret_cast<const void*>(&splitk_kernel<Policy>); }
   static int prepare() {
@@ -462,8 +523,7 @@ inline int fill_common(DecodeParams& p, const char* who, const void* q, int q_dt
   TKV_REQUIRE(!partials || (acc && m && l), TKV_ERR_INVALID,
               "%s: partial buffers (acc, m, l) required", who);
   TKV_REQUIRE(partials || out, TKV_ERR_INVALID, "%s: out required", who);
-  TKV_REQUIRE(q_dtype != TKV_DTYPE_F16 || ((uintptr_t)q & 7u) == 0, TKV_ERR_ALIGN,
-              "%s: q must be 8-byte aligned", who);
+  TKV_REQUIRE(aligned16(q), TKV_ERR_ALIGN, "%s: q must be 16-byte aligned", who);
   p.q = q;
   p.q_dtype = q_dtype;
   p.acc = acc;
