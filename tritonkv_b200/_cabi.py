@@ -88,8 +88,21 @@ def load():
     )
 
 
+_available_ok: tuple[bool, str] | None = None
+
+
 def available() -> tuple[bool, str]:
     """(usable, why): the library loads and a CUDA device is present."""
+    global _available_ok
+    if _available_ok is not None:
+        return _available_ok
+    r = _available()
+    if r[0]:
+        _available_ok = r  # a positive answer does not change during the process
+    return r
+
+
+def _available() -> tuple[bool, str]:
     try:
         lib = load()
     except RuntimeError as exc:
@@ -130,6 +143,29 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
 
 def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class on_device:
+    """``with on_device(dev):`` makes ``dev`` current for the C-ABI calls inside; when it
+    already is (the common case) this costs one integer compare instead of a device switch."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def ptr(t: torch.Tensor | None):

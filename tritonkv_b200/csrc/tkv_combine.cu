@@ -33,29 +33,73 @@ __global__ void __launch_bounds__(kCombineThreads)
   const float* lrow = l + (int64_t)row * ml_row;
   const float* arow = acc + (int64_t)row * a_row + d0 + dl * 4;
 
-  float mloc = -INFINITY;
-  for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s * ml_slot));
-#pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
-  if (lane == 0) red_m[warp] = mloc;
-  __syncthreads();
-  float M = red_m[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
+  pdl_wait();  // partials come from the kernel launched just before this one
 
+  constexpr int kCached = 8;  // slots per thread kept in registers: NS <= 256
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
   float L = 0.f;
+  float M;
+  if (NS <= 32 * kCached) {
+    // All loads are issued before the block-wide maximum is known, so their latency
+    // overlaps the reduction instead of following it.
+    float ms[kCached], ls[kCached];
+    float4 xs[kCached];
+    float mloc = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kCached; ++i) {
+      const int s = sg + 32 * i;
+      ms[i] = -INFINITY;
+      ls[i] = 0.f;
+      xs[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s < NS) {
+        ms[i] = __ldg(mrow + s * ml_slot);
+        ls[i] = __ldg(lrow + s * ml_slot);
+        xs[i] = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
+        mloc = fmaxf(mloc, ms[i]);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+      mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
+    if (lane == 0) red_m[warp] = mloc;
+    __syncthreads();
+    M = red_m[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
+#pragma unroll
+    for (int i = 0; i < kCached; ++i) {
+      if (ms[i] > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never use it
+        const float w = ex2(ms[i] - M);
+        a.x = fmaf(w, xs[i].x, a.x);
+        a.y = fmaf(w, xs[i].y, a.y);
+        a.z = fmaf(w, xs[i].z, a.z);
+        a.w = fmaf(w, xs[i].w, a.w);
+        L = fmaf(w, ls[i], L);
+      }
+    }
+  } else {
+    float mloc = -INFINITY;
+    for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s * ml_slot));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+      mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
+    if (lane == 0) red_m[warp] = mloc;
+    __syncthreads();
+    M = red_m[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
 #pragma unroll 4
-  for (int s = sg; s < NS; s += 32) {
-    const float ms = __ldg(mrow + s * ml_slot);
-    if (ms > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never read it
-      const float w = ex2(ms - M);
-      const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
-      a.x = fmaf(w, x.x, a.x);
-      a.y = fmaf(w, x.y, a.y);
-      a.z = fmaf(w, x.z, a.z);
-      a.w = fmaf(w, x.w, a.w);
-      L = fmaf(w, __ldg(lrow + s * ml_slot), L);
+    for (int s = sg; s < NS; s += 32) {
+      const float ms = __ldg(mrow + s * ml_slot);
+      if (ms > -INFINITY) {
+        const float w = ex2(ms - M);
+        const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
+        a.x = fmaf(w, x.x, a.x);
+        a.y = fmaf(w, x.y, a.y);
+        a.z = fmaf(w, x.z, a.z);
+        a.w = fmaf(w, x.w, a.w);
+        L = fmaf(w, __ldg(lrow + s * ml_slot), L);
+      }
     }
   }
   // the 4 split groups of a warp (lanes dl, dl+8, dl+16, dl+24)
@@ -110,6 +154,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kSmallWarps + warp;
   if (row >= rows) return;
+  pdl_wait();  // partials come from the kernel launched just before this one
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
   float ms[kSmallMaxNS];
@@ -153,6 +198,26 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
 
 }  // namespace tkv
 
+namespace {
+// Launch with programmatic stream serialisation: the kernel may begin while its
+// predecessor in the stream is still running and blocks at pdl_wait().
+template <typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+}  // namespace
+
 extern "C" int tkv_combine_strided(const float* acc, const float* m, const float* l, float* out,
                                    float* out_m, float* out_l, int64_t rows, int NS, int D,
                                    int64_t acc_row_stride, int64_t acc_slot_stride,
@@ -169,17 +234,15 @@ extern "C" int tkv_combine_strided(const float* acc, const float* m, const float
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
   if (NS <= kSmallMaxNS && rows >= 256) {
     const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
-    combine_small_kernel<<<blocks, kSmallWarps * 32, 0, (cudaStream_t)stream>>>(
-        acc, m, l, out, out_m, out_l, (int)rows, NS, D, acc_row_stride, acc_slot_stride,
-        ml_row_stride, ml_slot_stride);
-    TKV_CUDA(cudaGetLastError());
+    TKV_CUDA(launch_pdl(tkv::combine_small_kernel, dim3(blocks), dim3(kSmallWarps * 32),
+                        (cudaStream_t)stream, acc, m, l, out, out_m, out_l, (int)rows, NS, D,
+                        acc_row_stride, acc_slot_stride, ml_row_stride, ml_slot_stride));
     return TKV_OK;
   }
   dim3 grid((unsigned)rows, D / kCombineSlice);
-  combine_kernel<<<grid, kCombineThreads, 0, (cudaStream_t)stream>>>(
-      acc, m, l, out, out_m, out_l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
-      ml_slot_stride);
-  TKV_CUDA(cudaGetLastError());
+  TKV_CUDA(launch_pdl(tkv::combine_kernel, grid, dim3(kCombineThreads), (cudaStream_t)stream, acc, m,
+                      l, out, out_m, out_l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
+                      ml_slot_stride));
   return TKV_OK;
 }
 

@@ -117,12 +117,13 @@ struct Fp16Policy {
     const int k_c = lane >> 4;
     float (&sc)[4] = out.s;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sc[i] = 0.f;
-#pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
       uint32_t r[4];
       ldmatrix_x4(r, st + chunk_off(k_r, 2 * ch + k_c));
-      mma16816(sc, r[0], r[1], r[2], r[3], qq.qf[ch][0], qq.qf[ch][1]);
+      if (ch == 0)
+        mma16816_zero(sc, r[0], r[1], r[2], r[3], qq.qf[ch][0], qq.qf[ch][1]);
+      else
+        mma16816(sc, r[0], r[1], r[2], r[3], qq.qf[ch][0], qq.qf[ch][1]);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) sc[i] *= qk_scale;

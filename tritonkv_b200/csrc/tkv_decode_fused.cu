@@ -278,10 +278,9 @@ struct FusedPolicy {
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt) {
     float c[NACC][4];
+    bool started[NACC];  // resolved at compile time: the loops below are fully unrolled
 #pragma unroll
-    for (int a = 0; a < NACC; ++a)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) c[a][i] = 0.f;
+    for (int a = 0; a < NACC; ++a) started[a] = false;
 #pragma unroll
     for (int bb = 0; bb < NBLK; bb += 2) {
       uint32_t r[4];
@@ -301,13 +300,20 @@ struct FusedPolicy {
           constexpr uint32_t M0 = C::MASK0;
           const uint32_t mask = M0 << (NBITS * pp);
           const int ch = pp * NBLK + blk;
-          mma16816(c[(16 * ch) / ACC_DIMS], xl & mask, xh & mask, xl8 & mask, xh8 & mask,
-                   qq.qf[ch][0], qq.qf[ch][1]);
+          const int a = (16 * ch) / ACC_DIMS;
+          if (!started[a]) {
+            mma16816_zero(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
+                          qq.qf[ch][1]);
+            started[a] = true;
+          } else {
+            mma16816(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
+                     qq.qf[ch][1]);
+          }
         }
       }
     }
     // zero-point term: sum_g z[token][g] * qsum[g][head]
-    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+    float s4[4];
     {
       const __half* kz_t = kz_s + mt * 16 * NG;
       uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
@@ -321,7 +327,7 @@ struct FusedPolicy {
         a2 = pack_half2(z0, z0);
         a3 = pack_half2(z1, z1);
       }
-      mma16816(s4, a0, a1, a2, a3, qq.qz0, qq.qz1);
+      mma16816_zero(s4, a0, a1, a2, a3, qq.qz0, qq.qz1);
     }
     // scale term
     {

@@ -151,6 +151,9 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
+  // The whole grid is resident at once, so the combine kernel that follows may be
+  // scheduled right away; it waits for this grid's completion before it reads anything.
+  pdl_launch_dependents();
 
   uint8_t* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
   const uint32_t ring_u32 = smem_u32(ring);

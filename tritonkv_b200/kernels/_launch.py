@@ -157,7 +157,7 @@ def combine_splits(acc: torch.Tensor, maxs: torch.Tensor, sums: torch.Tensor,
     out = check_out(out, B, HQ, D, acc.device)
     if (out_m is None) != (out_l is None):
         raise ValueError("out_m and out_l must be given together")
-    with torch.cuda.device(acc.device):
+    with _cabi.on_device(acc.device):
         _cabi.check(lib.tkv_combine(acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(),
                                     out.data_ptr(), _cabi.ptr(out_m), _cabi.ptr(out_l), B, HQ, NS,
                                     D, _cabi.stream_ptr(acc.device)))

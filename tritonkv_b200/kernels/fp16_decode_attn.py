@@ -58,7 +58,7 @@ def fp16_decode_attention(
     seq_lens = check_seq_lens(seq_lens, B, device)
 
     lib = _cabi.load()
-    with torch.cuda.device(device):
+    with _cabi.on_device(device):
         ragged = seq_lens is not None
         target = None
         if num_splits is None and ragged:
