@@ -19,7 +19,8 @@ _lib = None
 def load():
     global _lib
     if _lib is None:
-        if not os.path.exists(_LIB):
+        src = os.path.join(_HERE, "tkv_oracle.c")
+        if not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
             subprocess.run(["make", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
         lib = ctypes.CDLL(_LIB)
         lib.tkvo_num_threads.restype = ctypes.c_int
@@ -33,6 +34,16 @@ def _p(a):
 
 def num_threads() -> int:
     return load().tkvo_num_threads()
+
+
+def use_all_cores() -> int:
+    """Use every host core the process may run on, whatever OMP_NUM_THREADS says."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    load().tkvo_set_num_threads(n)
+    return num_threads()
 
 
 def pack_codes(codes, nbits):
