@@ -46,7 +46,13 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the split kernel from the
 # ncu capture summarised under profiles/ (None until a capture for that cell exists).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.04 MB read + 0 written
+    "qwen-b1/4b/ctx65536": 21_043_200,
+    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.09 MB read + 3.0 MB written) at batch 16,
+    # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.3 %)
+    "llama8b-b64/4b/ctx4096": 4 * (84_087_040 + 2_990_000),
+}
 
 
 def parse_args():
