@@ -397,3 +397,81 @@ def test_history_split_merge_emulated_on_one_gpu(world):
         combine(ws["acc"], ws["maxs"], ws["sums"], out=acc, out_m=m, out_l=l)
     got = P.merge_gathered(gathered, B, HQ, D)
     assert_close(got, oracle_attention(q, kq, vq), f"history split over {world} ranks")
+
+
+# ------------------------------------------------------------------ benchmark configurations
+
+
+def _ragged_grid():
+    for D in (64, 128):
+        for HQ, HKV in ((8, 1), (32, 8)):
+            for nbits in (2, 4):
+                for gs in (32, 64, 128):
+                    if gs <= D:  # gs=128 with D=64 is invalid in the reference too (quantize.py:200)
+                        yield D, HQ, HKV, nbits, gs
+
+
+@pytest.mark.parametrize("D,HQ,HKV,nbits,gs", list(_ragged_grid()))
+def test_ragged_sweep_grid(D, HQ, HKV, nbits, gs):
+    """The ragged batched sweep (batch 16, per-sequence lengths from a seed, 1 % of the K
+    entries x20) over its whole (D, heads, nbits, group) grid, at lengths the oracle does
+    in a second (the full lengths are covered by the property test below)."""
+    from tritonkv_b200.workloads import make_entry_outlier_k
+
+    B, S = 16, 1536
+    lens = ragged_seq_lens(B, 48, S, seed=D + HQ + nbits + gs)
+    q, k, v = make_entry_outlier_k(B, HQ, HKV, S, D, device=DEV, seed=7, frac=0.01, factor=20.0)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    got = fused_decode_attention(q, kq, vq, seq_lens=lens.to(DEV))
+    assert_close(got, oracle_attention(q, kq, vq, seq_lens=lens), f"ragged D={D} {HQ}/{HKV} {nbits}b gs={gs}")
+
+
+def test_ragged_full_lengths_properties():
+    """Ragged batch at the sweep's full lengths (1024..32768): each sequence's output
+    equals a dense call on that sequence alone cut to its length (bit-for-bit geometry
+    differs, so within the kernel tolerance), and padding beyond seq_lens is never read
+    (poisoning it with NaN scale/zero changes nothing)."""
+    B, HQ, HKV, D = 4, 32, 8, 128
+    lens = torch.tensor([32768, 1024, 20011, 7], dtype=torch.int32)
+    S = 32768
+    g = torch.Generator(device=DEV).manual_seed(5)
+    q = torch.randn(B, HQ, D, generator=g, device=DEV).half()
+    k = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    v = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    out = fused_decode_attention(q, kq, vq, seq_lens=lens.to(DEV))
+    for b in range(B):
+        n = int(lens[b])
+        cut = lambda t: Q.QuantizedTensor(t.packed[b:b + 1, :, :n].contiguous(),
+                                          t.scale[b:b + 1, :, :n].contiguous(),
+                                          t.zero[b:b + 1, :, :n].contiguous(), 4, 32, D)
+        alone = fused_decode_attention(q[b:b + 1], cut(kq), cut(vq))
+        assert (out[b:b + 1] - alone).abs().max().item() < 2e-3
+    for b in range(B):  # poison everything past each sequence's end
+        n = int(lens[b])
+        for t in (kq, vq):
+            t.scale[b, :, n:] = float("nan")
+            t.zero[b, :, n:] = float("inf")
+            t.packed[b, :, n:] = 255
+    out2 = fused_decode_attention(q, kq, vq, seq_lens=lens.to(DEV))
+    assert torch.equal(out, out2)
+
+
+def test_llama70b_long_context_full_size():
+    """Llama-3-70B-shaped long-context decode at full size (HQ 64, HKV 8, ctx 131072,
+    2-bit, 100 MB of cache) against the C twin of the oracle."""
+    from oracle import c_oracle
+
+    B, HQ, HKV, S, D = 1, 64, 8, 131072, 128
+    g = torch.Generator(device=DEV).manual_seed(11)
+    q = torch.randn(B, HQ, D, generator=g, device=DEV).half()
+    k = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    v = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    kq, vq = Q.quantize_kv(k, v, 2, 32)
+    del k, v
+    got = fused_decode_attention(q, kq, vq)
+    c_oracle.use_all_cores()
+    h = lambda t: (t.cpu().numpy() if t.dtype == torch.uint8 else t.cpu().numpy().view(np.uint16))
+    ref = c_oracle.decode_step(q.float().cpu().numpy(), h(kq.packed), h(kq.scale), h(kq.zero),
+                               h(vq.packed), h(vq.scale), h(vq.zero), 2, 32)
+    assert_close(got, ref, "llama-70b ctx 131072 2-bit")
