@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(kCombineThreads)
   const float* lrow = l + (int64_t)row * ml_row;
   const float* arow = acc + (int64_t)row * a_row + d0 + dl * 4;
 
+  pdl_launch_dependents();  // the next kernel of the stream may start its prologue
   pdl_wait();  // partials come from the kernel launched just before this one
 
   constexpr int kCached = 8;  // slots per thread kept in registers: NS <= 256
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kSmallWarps + warp;
   if (row >= rows) return;
+  pdl_launch_dependents();  // the next kernel of the stream may start its prologue
   pdl_wait();  // partials come from the kernel launched just before this one
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
@@ -198,26 +200,6 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
 
 }  // namespace tkv
 
-namespace {
-// Launch with programmatic stream serialisation: the kernel may begin while its
-// predecessor in the stream is still running and blocks at pdl_wait().
-template <typename... Args>
-cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream,
-                       Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-}  // namespace
-
 extern "C" int tkv_combine_strided(const float* acc, const float* m, const float* l, float* out,
                                    float* out_m, float* out_l, int64_t rows, int NS, int D,
                                    int64_t acc_row_stride, int64_t acc_slot_stride,
@@ -234,14 +216,14 @@ extern "C" int tkv_combine_strided(const float* acc, const float* m, const float
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
   if (NS <= kSmallMaxNS && rows >= 256) {
     const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
-    TKV_CUDA(launch_pdl(tkv::combine_small_kernel, dim3(blocks), dim3(kSmallWarps * 32),
+    TKV_CUDA(launch_pdl(tkv::combine_small_kernel, dim3(blocks), dim3(kSmallWarps * 32), 0,
                         (cudaStream_t)stream, acc, m, l, out, out_m, out_l, (int)rows, NS, D,
                         acc_row_stride, acc_slot_stride, ml_row_stride, ml_slot_stride));
     return TKV_OK;
   }
   dim3 grid((unsigned)rows, D / kCombineSlice);
-  TKV_CUDA(launch_pdl(tkv::combine_kernel, grid, dim3(kCombineThreads), (cudaStream_t)stream, acc, m,
-                      l, out, out_m, out_l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
+  TKV_CUDA(launch_pdl(tkv::combine_kernel, grid, dim3(kCombineThreads), 0, (cudaStream_t)stream, acc,
+                      m, l, out, out_m, out_l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
                       ml_slot_stride));
   return TKV_OK;
 }

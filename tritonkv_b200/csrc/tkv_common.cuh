@@ -113,6 +113,26 @@ __device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
+// Host side: launch with programmatic stream serialisation.  The kernel may begin while
+// its predecessor in the stream is still running; it must call pdl_wait() before its
+// first global-memory access.  After an ordinary predecessor (one that never calls
+// pdl_launch_dependents) this behaves like a plain launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -204,6 +224,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // 2-D tiled TMA load of one box into this CTA's shared memory; completion is
 // signalled on `bar` as transferred bytes.  c0 = innermost coordinate (must be a
 // multiple of 16 bytes), c1 = row.
+// Warm the descriptor cache for a tensor map that lives in kernel-parameter space.
+__device__ __forceinline__ void prefetch_tensormap(const void* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map, int c0, int c1,
                                             uint32_t bar) {
   asm volatile(

@@ -44,6 +44,7 @@ struct Fp16Policy {
   };
 
   __device__ static void report_timeout() { atomicExch(&g_fp16_status, 1); }
+  __device__ static __forceinline__ void prefetch_maps(const Maps&) {}
 
   // Byte offset of the 16-byte chunk `c16` (0 .. ROW/16) of token row r inside a tile.
   __device__ static __forceinline__ uint32_t chunk_off(int r, int c16) {

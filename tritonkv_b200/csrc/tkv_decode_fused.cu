@@ -139,6 +139,10 @@ struct FusedPolicy {
   };
 
   __device__ static void report_timeout() { atomicExch(&g_fused_status, 1); }
+  __device__ static __forceinline__ void prefetch_maps(const Maps& maps) {
+    prefetch_tensormap(&maps.k);
+    prefetch_tensormap(&maps.v);
+  }
 
   // Fill one stage with the 32 tokens starting at global row `row`; `nvalid` of them
   // belong to the unit.

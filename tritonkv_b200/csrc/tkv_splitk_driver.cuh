@@ -32,7 +32,8 @@ namespace tkv {
 constexpr float kLazyTau = 4.0f;  // head-room of the lazily raised softmax exponent (log2 units)
 
 struct SplitSched {
-  int persistent;  // 1: balanced tile ranges; 0: CTA c <-> unit c (ragged batches)
+  int persistent;  // 0: CTA c <-> unit c (ragged batches); 1: balanced tile ranges over the
+                   // global tile sequence; 2: SEG CTAs per unit, ranges aligned to the unit
   int NS;          // history splits per sequence (unit boundaries)
   int TUf, TUl;    // tiles in a full split / in the last split
   int T_seq;       // tiles per sequence = (NS-1)*TUf + TUl
@@ -70,6 +71,19 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
     s.grid = (int)((T + s.TC - 1) / s.TC);
     s.SEG = (s.TUf - 1 + s.TC - 1) / s.TC + 1;
     if (s.TUf <= 1) s.SEG = 1;
+    // Few, long units (small batches): give every unit its own whole number of CTAs, so
+    // that no CTA straddles two units and pays a second query load and epilogue.  Taken
+    // when it lengthens the longest CTA by at most one tile.
+    if (units * 2 <= wave) {
+      const int cpu = (int)(wave / units);
+      const int TCu = (s.TUf + cpu - 1) / cpu;
+      if (TCu <= s.TC + 1) {
+        s.persistent = 2;
+        s.TC = TCu;
+        s.SEG = (s.TUf + TCu - 1) / TCu;
+        s.grid = (int)(units * s.SEG);
+      }
+    }
   }
   s.nslots = s.NS * s.SEG;
   return s;
@@ -154,6 +168,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // The whole grid is resident at once, so the combine kernel that follows may be
   // scheduled right away; it waits for this grid's completion before it reads anything.
   pdl_launch_dependents();
+  if (threadIdx.x == 0) Policy::prefetch_maps(maps);
 
   uint8_t* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
   const uint32_t ring_u32 = smem_u32(ring);
@@ -176,7 +191,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     }
     fence_barrier_init();
   }
-  __syncthreads();
   const int q_esz = p.q_dtype == TKV_DTYPE_F32 ? 4 : 2;
   auto prefetch_q = [&](int slot, int b, int hkv, int hc) {
     const int row_bytes = D * q_esz, cpr = row_bytes >> 4;
@@ -195,13 +209,47 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // ---- this CTA's tile range ----
   int g0, g1;
   Segment seg;
-  if (sc.persistent) {
+  if (sc.persistent == 1) {
     g0 = min(cta * sc.TC, sc.T);
     g1 = min(g0 + sc.TC, sc.T);
     if (g0 >= g1) return;
     seg = segment_at<kTok>(p, sc, g0, g1, cta);
+  } else if (sc.persistent == 2) {
+    // unit-aligned: CTA j of the unit's SEG takes tiles [j*TC, (j+1)*TC) of the unit
+    const int u = cta / sc.SEG, j = cta - u * sc.SEG;
+    const int bh = u / sc.NS;
+    seg.split = u - bh * sc.NS;
+    seg.b = bh / sc.HKVc;
+    const int hk = bh - seg.b * sc.HKVc;
+    seg.hkv = hk / p.hchunks;
+    seg.hc = hk - seg.hkv * p.hchunks;
+    const int TU = (seg.split == sc.NS - 1) ? sc.TUl : sc.TUf;
+    const int t0 = j * sc.TC;
+    const int lo_unit = seg.split * p.split_size;
+    seg.hi = min(lo_unit + p.split_size, p.S);
+    seg.lo_tok = lo_unit + t0 * kTok;
+    seg.ntiles = min(sc.TC, TU - t0);
+    seg.slot = seg.split * sc.SEG + j;
+    seg.fill_from = seg.fill_to = -1;
+    g0 = 0;
+    g1 = seg.ntiles;
+    seg.g_end = g1;
+    if (seg.ntiles <= 0) {
+      // a shorter last split leaves this CTA without tiles: its slot is marked empty
+      pdl_wait();
+      if (threadIdx.x < kHeadsPerCta) {
+        const int hg = seg.hc * kHeadsPerCta + threadIdx.x;
+        if (hg < p.group) {
+          const int64_t hq = (int64_t)seg.b * p.HQ + seg.hkv * p.group + hg;
+          p.m[hq * sc.nslots + seg.slot] = -INFINITY;
+          p.l[hq * sc.nslots + seg.slot] = 0.f;
+        }
+      }
+      return;
+    }
   } else {
     // static: CTA <-> unit, per-sequence length from seq_lens
+    pdl_wait();
     const int bh = cta / sc.NS;
     seg.split = cta - bh * sc.NS;
     seg.b = bh / sc.HKVc;
@@ -220,6 +268,14 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     seg.g_end = g1;
   }
 
+  __syncthreads();  // barriers initialised
+  // Launched as a programmatic dependent: everything above ran while the previous kernel
+  // of the stream was finishing; global memory is touched only from here on.
+  pdl_wait();
+  // The query rows go first: behind the first tiles of every warp of the grid they would
+  // queue for microseconds, ahead of them they arrive while the tiles are being issued.
+  prefetch_q(0, seg.b, seg.hkv, seg.hc);
+
   // ---- issue cursor ----
   auto cursor_enter = [&](IssueCursor& c, const Segment& s, int seg_g) {
     c.seg_g = seg_g;
@@ -233,7 +289,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   cursor_enter(cur, seg, g0);
   auto cursor_skip_empty = [&]() {
     // move to the next segment in which this warp has a tile (persistent mode only)
-    while (cur.cnt == 0 && sc.persistent && cur.g_end < g1) {
+    while (cur.cnt == 0 && sc.persistent == 1 && cur.g_end < g1) {
       const int g = cur.g_end;
       const Segment s = segment_at<kTok>(p, sc, g, g1, cta);
       cursor_enter(cur, s, g);
@@ -259,8 +315,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   };
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue_next();
-  prefetch_q(0, seg.b, seg.hkv, seg.hc);
-  if (sc.persistent && seg.g_end < g1) {
+  if (sc.persistent == 1 && seg.g_end < g1) {
     const Segment s1 = segment_at<kTok>(p, sc, seg.g_end, g1, cta);
     prefetch_q(1, s1.b, s1.hkv, s1.hc);
   }
@@ -330,35 +385,53 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     }
     if (lane == 0) s_slot[warp] = (consumed + STAGES - 1) % STAGES;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < kHeadsPerCta * D; idx += WARPS * 32) {
-      const int h = idx / D, d = idx - h * D;
-      const int hg = seg.hc * kHeadsPerCta + h;
-      if (hg >= p.group) continue;
-      float M = -INFINITY;
+    // Each thread merges float4 columns; per item the four warps' loads are independent
+    // (no data-dependent branch around them), so they overlap instead of serialising.
+    {
+      constexpr int D4 = D / 4;
+      constexpr int ITEMS = kHeadsPerCta * D4;
+      static_assert(ITEMS % (WARPS * 32) == 0, "merge items must tile the CTA");
+      uint32_t voff[WARPS];
 #pragma unroll
-      for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w][h]);
-      float a = 0.f, L = 0.f;
+      for (int w = 0; w < WARPS; ++w) voff[w] = (uint32_t)((w * STAGES + s_slot[w]) * STAGE_BYTES);
 #pragma unroll
-      for (int w = 0; w < WARPS; ++w) {
-        const float mw = s_m[w][h];
-        if (mw != -INFINITY) {
-          const float s = ex2(mw - M);
-          const float* v = reinterpret_cast<const float*>(
-              smem + ((size_t)w * STAGES + s_slot[w]) * STAGE_BYTES);
-          a = fmaf(s, v[h * D + d], a);
+      for (int it = 0; it < ITEMS / (WARPS * 32); ++it) {
+        const int idx = it * (WARPS * 32) + threadIdx.x;
+        const int h = idx / D4, d = (idx - h * D4) * 4;
+        const int hg = seg.hc * kHeadsPerCta + h;
+        if (hg >= p.group) continue;
+        float mw[WARPS], M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+          mw[w] = s_m[w][h];
+          M = fmaxf(M, mw[w]);
+        }
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+          const bool live = mw[w] != -INFINITY;  // a warp without tiles left its stage unwritten
+          const float s = live ? ex2(mw[w] - M) : 0.f;
+          const float4 v = *reinterpret_cast<const float4*>(smem + voff[w] + (h * D + d) * 4);
+          a.x = fmaf(s, live ? v.x : 0.f, a.x);
+          a.y = fmaf(s, live ? v.y : 0.f, a.y);
+          a.z = fmaf(s, live ? v.z : 0.f, a.z);
+          a.w = fmaf(s, live ? v.w : 0.f, a.w);
           L = fmaf(s, s_l[w][h], L);
         }
-      }
-      const int64_t hq = (int64_t)seg.b * p.HQ + seg.hkv * p.group + hg;
-      if (p.partials) {
-        const int64_t pi = hq * sc.nslots + seg.slot;
-        p.acc[pi * D + d] = a;
-        if (d == 0) {
-          p.m[pi] = M;
-          p.l[pi] = L;
+        const int64_t hq = (int64_t)seg.b * p.HQ + seg.hkv * p.group + hg;
+        if (p.partials) {
+          const int64_t pi = hq * sc.nslots + seg.slot;
+          *reinterpret_cast<float4*>(p.acc + pi * D + d) = a;
+          if (d == 0) {
+            p.m[pi] = M;
+            p.l[pi] = L;
+          }
+        } else {
+          const float inv = (L > 0.f) ? 1.f / L : 0.f;
+          *reinterpret_cast<float4*>(p.out + hq * D + d) =
+              make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         }
-      } else {
-        p.out[hq * D + d] = (L > 0.f) ? a / L : 0.f;
       }
     }
     if (seg.fill_from >= 0) {
@@ -377,7 +450,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     __syncthreads();
     need_proxy_fence = true;
 
-    if (!sc.persistent) break;
+    if (sc.persistent != 1) break;
     g = seg.g_end;
     if (g >= g1 || timed_out) break;
     seg = segment_at<kTok>(p, sc, g, g1, cta);
@@ -482,8 +555,11 @@ struct SplitLaunch {
                     cudaStream_t stream) {
     int rc = prepare();
     if (rc != TKV_OK) return rc;
-    splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem_bytes(), stream>>>(maps, p, sc);
-    TKV_CUDA(cudaGetLastError());
+    // Programmatic dependent launch: the prologue (barrier set-up, schedule arithmetic)
+    // overlaps the tail of the previous kernel of the stream; the kernel itself waits for
+    // that kernel's completion before its first global access.
+    TKV_CUDA(launch_pdl(splitk_kernel<Policy>, dim3(sc.grid), dim3(Policy::WARPS * 32),
+                        (size_t)smem_bytes(), stream, maps, p, sc));
     return TKV_OK;
   }
   static int attrs(int* regs, int* smem, int* local, int* ctas) {
@@ -527,6 +603,8 @@ inline int fill_common(DecodeParams& p, const char* who, const void* q, int q_dt
               "%s: partial buffers (acc, m, l) required", who);
   TKV_REQUIRE(partials || out, TKV_ERR_INVALID, "%s: out required", who);
   TKV_REQUIRE(aligned16(q), TKV_ERR_ALIGN, "%s: q must be 16-byte aligned", who);
+  TKV_REQUIRE(aligned16(acc) && aligned16(out), TKV_ERR_ALIGN,
+              "%s: acc and out must be 16-byte aligned", who);
   p.q = q;
   p.q_dtype = q_dtype;
   p.acc = acc;
