@@ -41,23 +41,23 @@ __global__ void __launch_bounds__(kCombineThreads)
   float L = 0.f;
   float M;
   if (NS <= 32 * kCached) {
-    // All loads are issued before the block-wide maximum is known, so their latency
-    // overlaps the reduction instead of following it.
+    // All loads are issued back to back, before any of them is used and before the
+    // block-wide maximum is known: one round trip to L2 instead of one per slot.  Slots
+    // past NS re-read the last slot (always in bounds) and are discarded.
     float ms[kCached], ls[kCached];
     float4 xs[kCached];
+#pragma unroll
+    for (int i = 0; i < kCached; ++i) {
+      const int s = min(sg + 32 * i, NS - 1);
+      ms[i] = __ldg(mrow + s * ml_slot);
+      ls[i] = __ldg(lrow + s * ml_slot);
+      xs[i] = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
+    }
     float mloc = -INFINITY;
 #pragma unroll
     for (int i = 0; i < kCached; ++i) {
-      const int s = sg + 32 * i;
-      ms[i] = -INFINITY;
-      ls[i] = 0.f;
-      xs[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (s < NS) {
-        ms[i] = __ldg(mrow + s * ml_slot);
-        ls[i] = __ldg(lrow + s * ml_slot);
-        xs[i] = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
-        mloc = fmaxf(mloc, ms[i]);
-      }
+      if (sg + 32 * i >= NS) ms[i] = -INFINITY;
+      mloc = fmaxf(mloc, ms[i]);
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1)
@@ -159,31 +159,42 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
   pdl_wait();  // partials come from the kernel launched just before this one
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
-  float ms[kSmallMaxNS];
+  // loads first, uses afterwards: one round trip for (m, l), one for the acc rows
+  float ms[kSmallMaxNS], ls[kSmallMaxNS];
+#pragma unroll
+  for (int s = 0; s < kSmallMaxNS; ++s) {
+    const int sc = min(s, NS - 1);
+    ms[s] = __ldg(mrow + sc * ml_slot);
+    ls[s] = __ldg(lrow + sc * ml_slot);
+  }
   float M = -INFINITY;
 #pragma unroll
   for (int s = 0; s < kSmallMaxNS; ++s) {
-    ms[s] = s < NS ? __ldg(mrow + s * ml_slot) : -INFINITY;
+    if (s >= NS) ms[s] = -INFINITY;
     M = fmaxf(M, ms[s]);
   }
   float L = 0.f;
 #pragma unroll
   for (int s = 0; s < kSmallMaxNS; ++s) {
     ms[s] = (ms[s] > -INFINITY) ? ex2(ms[s] - M) : 0.f;  // weight of slot s
-    if (s < NS && ms[s] > 0.f) L = fmaf(ms[s], __ldg(lrow + s * ml_slot), L);
+    if (ms[s] > 0.f) L = fmaf(ms[s], ls[s], L);
   }
   const float inv = (out_m == nullptr) ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
   for (int v = lane; v < (D >> 2); v += 32) {
+    float4 x[kSmallMaxNS];
+#pragma unroll
+    for (int s = 0; s < kSmallMaxNS; ++s) {
+      const int sc = min(s, NS - 1);
+      x[s] = __ldg(reinterpret_cast<const float4*>(acc + (int64_t)row * a_row + sc * a_slot) + v);
+    }
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int s = 0; s < kSmallMaxNS; ++s) {
-      if (s < NS && ms[s] > 0.f) {  // empty slots may hold anything in acc: never read it
-        const float4 x =
-            __ldg(reinterpret_cast<const float4*>(acc + (int64_t)row * a_row + s * a_slot) + v);
-        a.x = fmaf(ms[s], x.x, a.x);
-        a.y = fmaf(ms[s], x.y, a.y);
-        a.z = fmaf(ms[s], x.z, a.z);
-        a.w = fmaf(ms[s], x.w, a.w);
+      if (s < NS && ms[s] > 0.f) {  // empty slots may hold anything in acc: never use it
+        a.x = fmaf(ms[s], x[s].x, a.x);
+        a.y = fmaf(ms[s], x[s].y, a.y);
+        a.z = fmaf(ms[s], x[s].z, a.z);
+        a.w = fmaf(ms[s], x[s].w, a.w);
       }
     }
     a.x *= inv;

@@ -76,6 +76,33 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, ui
                : "r"(addr));
 }
 
+// Shared-memory accesses by 32-bit shared address (no generic-address arithmetic).
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_v2f(uint32_t addr, float x, float y) {
+  asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(addr), "f"(x), "f"(y) : "memory");
+}
+
 // Transpose an 8x8 matrix of 16-bit elements held one 32-bit register per lane
 // (lane 4r+c holds row r, columns 2c and 2c+1).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
@@ -221,13 +248,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
-// 2-D tiled TMA load of one box into this CTA's shared memory; completion is
-// signalled on `bar` as transferred bytes.  c0 = innermost coordinate (must be a
-// multiple of 16 bytes), c1 = row.
 // Warm the descriptor cache for a tensor map that lives in kernel-parameter space.
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
+// 2-D tiled TMA load of one box into this CTA's shared memory; completion is
+// signalled on `bar` as transferred bytes.  c0 = innermost coordinate (must be a
+// multiple of 16 bytes), c1 = row.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map, int c0, int c1,
                                             uint32_t bar) {
   asm volatile(

@@ -57,8 +57,8 @@ struct FusedCfg {
   static constexpr int NBLK = DP / 16;         // 16-byte column blocks per token row
   static constexpr int NCH = D / 16;           // 16-dim chunks
   static constexpr int NG = D / GS;            // quantisation groups per token
-  static constexpr int ACC_DIMS = (GS < DP) ? GS : DP;  // dims sharing one score accumulator
-  static constexpr int NACC = D / ACC_DIMS;
+  static constexpr int ACC_DIMS = GS;  // dims sharing one score accumulator: a quantisation group
+  static constexpr int NACC = NG;
   static constexpr int CODE_BYTES = (kTok * DP + 1023) / 1024 * 1024;  // keeps V's swizzle phase
   static constexpr int NPAIR = (NBLK + 1) / 2;  // ldmatrix issues per 16-token half
   static constexpr int META_BYTES = kTok * NG * 2;
@@ -96,6 +96,22 @@ __device__ __forceinline__ MetaRow<NG> load_meta_row(const __half* p) {
   return r;
 }
 template <int NG>
+__device__ __forceinline__ MetaRow<NG> lds_meta_row(uint32_t addr) {
+  MetaRow<NG> r;
+  if constexpr (NG == 8) {
+    const uint4 v = lds_v4(addr);
+    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+  } else if constexpr (NG == 4) {
+    const uint2 v = lds_v2(addr);
+    r.w[0] = v.x; r.w[1] = v.y;
+  } else if constexpr (NG == 2) {
+    r.w[0] = lds_u32(addr);
+  } else {
+    r.w[0] = lds_u16(addr);
+  }
+  return r;
+}
+template <int NG>
 __device__ __forceinline__ float meta_f32(const MetaRow<NG>& r, int i) {
   const __half2 h = *reinterpret_cast<const __half2*>(&r.w[i >> 1]);
   return (i & 1) ? __high2float(h) : __low2float(h);
@@ -126,16 +142,20 @@ struct FusedPolicy {
     CUtensorMap k, v;
   };
   struct Query {
-    uint32_t qf[NCH][2];  // B operand of the score MMA
-    uint32_t qz0, qz1;    // B operand of the K zero-point MMA (hi/lo split of the group sums of q)
+    uint32_t qf[NCH][2];  // B operand of the score MMA; bit slice p is pre-scaled by 2^(-NBITS p)
+    uint32_t qz0, qz1;    // B operand of the K zero-point MMA: f16 hi / lo parts of
+                          // qk_scale * (sum of q over a group), groups 2t and 2t+1
     uint32_t off[2][C::NPAIR];  // this lane's ldmatrix byte offsets inside a code tile
+    uint32_t o_row;   // byte offset of token g's row inside a scale array
+    uint32_t o_kz;    // byte offset of this lane's K zero-point word (token g)
+    uint32_t o_vz;    // byte offset of this lane's first V zero-point (token 2t, group g mod NG)
+    uint32_t ones;    // (1, 1) in f16 on lanes 0-3: row 8 of the zero-point MMA sums the p's
   };
   struct Accum {
-    float m_ref0, m_ref1;    // exponent the probabilities refer to
-    float m_true0, m_true1;  // true running maxima
-    float l0, l1;            // per-lane partial sums of p
+    float m_ref0, m_ref1;    // exponent the probabilities refer to (same on the 8 lanes of a head)
+    float m_true0, m_true1;  // this lane's running maxima (reduced over lanes in finalize)
     float acc[NCH][4];
-    float zacc[4];
+    float zacc[4];  // rows 0..NG-1: sum_n p_n z_n[group]; row 8: sum_n p_n
   };
 
   __device__ static void report_timeout() { atomicExch(&g_fused_status, 1); }
@@ -214,7 +234,13 @@ struct FusedPolicy {
           qq.off[mt][pr] = Ls << 4;
         }
     }
+    qq.o_row = g * NG * 2;
+    qq.o_kz = (NG >= 2) ? (g * NG + ((2 * t) % NG)) * 2 : g * 2;
+    qq.o_vz = ((2 * t) * NG + (g % NG)) * 2;
+    qq.ones = (lane < 4) ? 0x3C003C00u : 0u;
+
     const uint8_t* qrow = qsm + g * D * (p.q_dtype == TKV_DTYPE_F32 ? 4 : 2);
+    const uint32_t qrow_s = smem_u32(qrow);
     float gsum[NG];
 #pragma unroll
     for (int i = 0; i < NG; ++i) gsum[i] = 0.f;
@@ -222,14 +248,23 @@ struct FusedPolicy {
     for (int ch = 0; ch < NCH; ++ch) {
       __half x[4];
       if (p.q_dtype == TKV_DTYPE_F16) {
-        *reinterpret_cast<uint2*>(x) =
-            *reinterpret_cast<const uint2*>(qrow + (16 * ch + 4 * t) * 2);
+        const uint2 v = lds_v2(qrow_s + (16 * ch + 4 * t) * 2);
+        *reinterpret_cast<uint2*>(x) = v;
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) x[i] = load_q_half(qrow, p.q_dtype, 16 * ch + 4 * t + i);
       }
-      qq.qf[ch][0] = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
-      qq.qf[ch][1] = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
+      // The code field of bit slice p is the f16 number c * 2^(NBITS p - 24); scaling the
+      // query down by the same power of two (exact unless |q| < 2^-14 2^(NBITS p), where the
+      // absolute error stays below 2^-25) lets every slice share one accumulator and scale.
+      const int slice = ch / NBLK;
+      const __half2 down = __float2half2_rn(pow2i(-NBITS * slice));
+      const uint32_t u0 = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
+      const uint32_t u1 = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
+      const __half2 v0 = __hmul2(*reinterpret_cast<const __half2*>(&u0), down);
+      const __half2 v1 = __hmul2(*reinterpret_cast<const __half2*>(&u1), down);
+      qq.qf[ch][0] = *reinterpret_cast<const uint32_t*>(&v0);
+      qq.qf[ch][1] = *reinterpret_cast<const uint32_t*>(&v1);
       gsum[(16 * ch) / GS] += (__half2float(x[0]) + __half2float(x[1])) +
                               (__half2float(x[2]) + __half2float(x[3]));
     }
@@ -238,23 +273,29 @@ struct FusedPolicy {
       gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 1);
       gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 2);
     }
-    // k-slots (2t, 2t+1) carry the f16 hi/lo split of the query sum of group t,
-    // k-slots (2t+8, 2t+9) that of group t+4.
-    qq.qz0 = 0;
-    qq.qz1 = 0;
+    // k-slots 2t, 2t+1 carry the f16 high parts of qk_scale * qsum of groups 2t, 2t+1,
+    // k-slots 2t+8, 2t+9 the low parts (the zero-point words are fed to both halves).
+    __half hi0 = __float2half(0.f), hi1 = hi0, lo0 = hi0, lo1 = hi0;
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
-      const __half hi16 = __float2half_rn(gsum[i]);
-      const __half lo16 = __float2half_rn(gsum[i] - __half2float(hi16));
-      const uint32_t v = pack_half2(hi16, lo16);
-      if (i == t) qq.qz0 = v;
-      if (i == t + 4) qq.qz1 = v;
+      const float v = gsum[i] * p.qk_scale;
+      const __half hi16 = __float2half_rn(v);
+      const __half lo16 = __float2half_rn(v - __half2float(hi16));
+      if (i == 2 * t) {
+        hi0 = hi16;
+        lo0 = lo16;
+      }
+      if (i == 2 * t + 1) {
+        hi1 = hi16;
+        lo1 = lo16;
+      }
     }
+    qq.qz0 = pack_half2(hi0, hi1);
+    qq.qz1 = pack_half2(lo0, lo1);
   }
 
   __device__ static __forceinline__ void reset(Accum& ac) {
     ac.m_ref0 = ac.m_ref1 = ac.m_true0 = ac.m_true1 = -INFINITY;
-    ac.l0 = ac.l1 = 0.f;
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
@@ -270,204 +311,210 @@ struct FusedPolicy {
   // Scores of one 32-token tile in stage `st` (scaled by qk_scale, tokens past the unit
   // end set to -inf); `left` = tokens from the tile start to the unit end.
   __device__ static __forceinline__ void scores(Scores& out, const Query& qq, uint32_t st,
-                                                const uint8_t* st_ptr, int left, float qk_scale,
+                                                const uint8_t*, int left, float qk_scale,
                                                 int lane) {
-    const int g = lane >> 2, t = lane & 3;
+    const int g = lane >> 2;
     const uint32_t kc = st;
-    const __half* ks_s = reinterpret_cast<const __half*>(st_ptr + 2 * C::CODE_BYTES);
-    const __half* kz_s = ks_s + kTok * NG;
+    const uint32_t ks_a = st + 2 * C::CODE_BYTES + qq.o_row;
+    const uint32_t kz_a = st + 2 * C::CODE_BYTES + C::META_BYTES + qq.o_kz;
+    const float qk24 = qk_scale * 16777216.f;  // the code fields carry 2^-24
+    constexpr int HALF = 16 * NG * 2;           // bytes of 16 token rows in a metadata array
 
-  // ================= scores for the two 16-token halves ============================
-  float (&sc)[2][4] = out.s;
+    float (&sc)[2][4] = out.s;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
-    float c[NACC][4];
-    bool started[NACC];  // resolved at compile time: the loops below are fully unrolled
+    for (int mt = 0; mt < 2; ++mt) {
+      float c[NACC][4];
+      bool started[NACC];  // resolved at compile time: the loops below are fully unrolled
 #pragma unroll
-    for (int a = 0; a < NACC; ++a) started[a] = false;
+      for (int a = 0; a < NACC; ++a) started[a] = false;
 #pragma unroll
-    for (int bb = 0; bb < NBLK; bb += 2) {
-      uint32_t r[4];
-      if constexpr (NBLK >= 2) {
-        ldmatrix_x4(r, kc + qq.off[mt][bb >> 1]);
-      } else {
-        ldmatrix_x2(r[0], r[1], kc + qq.off[mt][0]);
-        r[2] = r[3] = 0;
-      }
+      for (int bb = 0; bb < NBLK; bb += 2) {
+        uint32_t r[4];
+        if constexpr (NBLK >= 2) {
+          ldmatrix_x4(r, kc + qq.off[mt][bb >> 1]);
+        } else {
+          ldmatrix_x2(r[0], r[1], kc + qq.off[mt][0]);
+          r[2] = r[3] = 0;
+        }
 #pragma unroll
-      for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
-        const int blk = bb + jj;
-        const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
-        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+        for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
+          const int blk = bb + jj;
+          const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
+          const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
 #pragma unroll
-        for (int pp = 0; pp < P; ++pp) {
-          constexpr uint32_t M0 = C::MASK0;
-          const uint32_t mask = M0 << (NBITS * pp);
-          const int ch = pp * NBLK + blk;
-          const int a = (16 * ch) / ACC_DIMS;
-          if (!started[a]) {
-            mma16816_zero(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
-                          qq.qf[ch][1]);
-            started[a] = true;
-          } else {
-            mma16816(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
-                     qq.qf[ch][1]);
+          for (int pp = 0; pp < P; ++pp) {
+            constexpr uint32_t M0 = C::MASK0;
+            const uint32_t mask = M0 << (NBITS * pp);
+            const int ch = pp * NBLK + blk;
+            const int a = (16 * ch) / ACC_DIMS;
+            if (!started[a]) {
+              mma16816_zero(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
+                            qq.qf[ch][1]);
+              started[a] = true;
+            } else {
+              mma16816(c[a], xl & mask, xh & mask, xl8 & mask, xh8 & mask, qq.qf[ch][0],
+                       qq.qf[ch][1]);
+            }
           }
         }
       }
-    }
-    // zero-point term: sum_g z[token][g] * qsum[g][head]
-    float s4[4];
-    {
-      const __half* kz_t = kz_s + mt * 16 * NG;
-      uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-      if (t < NG) {
-        const __half z0 = kz_t[g * NG + t], z1 = kz_t[(g + 8) * NG + t];
-        a0 = pack_half2(z0, z0);
-        a1 = pack_half2(z1, z1);
+      // zero-point term (already times qk_scale): sum_g z[token][g] * qsum[g][head].  The
+      // word holding (z[2t], z[2t+1]) feeds k-slots 2t, 2t+1 (against the high parts) and
+      // 2t+8, 2t+9 (against the low parts); lanes past the last group re-read a valid word
+      // against a zero B operand.
+      float s4[4];
+      {
+        uint32_t zl, zh;
+        if constexpr (NG >= 2) {
+          zl = lds_u32(kz_a + mt * HALF);
+          zh = lds_u32(kz_a + mt * HALF + HALF / 2);
+        } else {
+          zl = lds_u16(kz_a + mt * HALF);
+          zh = lds_u16(kz_a + mt * HALF + HALF / 2);
+        }
+        mma16816_zero(s4, zl, zh, zl, zh, qq.qz0, qq.qz1);
       }
-      if constexpr (NG == 8) {
-        const __half z0 = kz_t[g * NG + t + 4], z1 = kz_t[(g + 8) * NG + t + 4];
-        a2 = pack_half2(z0, z0);
-        a3 = pack_half2(z1, z1);
+      // scale term
+      {
+        const MetaRow<NG> s_lo = lds_meta_row<NG>(ks_a + mt * HALF);
+        const MetaRow<NG> s_hi = lds_meta_row<NG>(ks_a + mt * HALF + HALF / 2);
+        float t4[4];
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const float f_lo = meta_f32<NG>(s_lo, a);
+          const float f_hi = meta_f32<NG>(s_hi, a);
+          if (a == 0) {
+            t4[0] = c[a][0] * f_lo;
+            t4[1] = c[a][1] * f_lo;
+            t4[2] = c[a][2] * f_hi;
+            t4[3] = c[a][3] * f_hi;
+          } else {
+            t4[0] = fmaf(c[a][0], f_lo, t4[0]);
+            t4[1] = fmaf(c[a][1], f_lo, t4[1]);
+            t4[2] = fmaf(c[a][2], f_hi, t4[2]);
+            t4[3] = fmaf(c[a][3], f_hi, t4[3]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[mt][i] = fmaf(t4[i], qk24, s4[i]);
       }
-      mma16816_zero(s4, a0, a1, a2, a3, qq.qz0, qq.qz1);
     }
-    // scale term
-    {
-      const MetaRow<NG> s_lo = load_meta_row<NG>(ks_s + (mt * 16 + g) * NG);
-      const MetaRow<NG> s_hi = load_meta_row<NG>(ks_s + (mt * 16 + g + 8) * NG);
+    if (left < kTok) {
 #pragma unroll
-      for (int a = 0; a < NACC; ++a) {
-        const int grp = (a * ACC_DIMS) / GS;
-        const int slice = (a * ACC_DIMS) / DP;
-        const float e = pow2i(24 - NBITS * slice);
-        const float f_lo = meta_f32<NG>(s_lo, grp) * e;
-        const float f_hi = meta_f32<NG>(s_hi, grp) * e;
-        s4[0] = fmaf(c[a][0], f_lo, s4[0]);
-        s4[1] = fmaf(c[a][1], f_lo, s4[1]);
-        s4[2] = fmaf(c[a][2], f_hi, s4[2]);
-        s4[3] = fmaf(c[a][3], f_hi, s4[3]);
+      for (int mt = 0; mt < 2; ++mt) {
+        if (mt * 16 + g >= left) sc[mt][0] = sc[mt][1] = -INFINITY;
+        if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
       }
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sc[mt][i] = s4[i] * qk_scale;
-  }
-  if (left < kTok) {
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      if (mt * 16 + g >= left) sc[mt][0] = sc[mt][1] = -INFINITY;
-      if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
-    }
-  }
   }
 
   // Online softmax update and O^T += V^T P^T for the tile whose scores are `in`.
   __device__ static __forceinline__ void update(Accum& ac, const Query& qq, Scores& in,
-                                                uint32_t st, uint8_t* st_ptr, int left, int lane) {
-    const int g = lane >> 2, t = lane & 3;
+                                                uint32_t st, uint8_t*, int left, int lane) {
     const uint32_t vc = st + C::CODE_BYTES;
-    const __half* vs_s = reinterpret_cast<const __half*>(st_ptr + 2 * C::CODE_BYTES) + 2 * kTok * NG;
-    const __half* vz_s = vs_s + kTok * NG;
+    const uint32_t vs_a = st + 2 * C::CODE_BYTES + 2 * C::META_BYTES + qq.o_row;
+    const uint32_t vz_a = st + 2 * C::CODE_BYTES + 3 * C::META_BYTES + qq.o_vz;
+    constexpr int HALF = 16 * NG * 2;
     float (&sc)[2][4] = in.s;
-  // ================= online softmax with a lazily raised reference exponent ========
-  {
-    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
-    float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+    // ---- online softmax with a lazily raised reference exponent ----
+    {
+      // this lane's maxima for heads 2t / 2t+1; the cross-lane maximum is only needed
+      // when some lane exceeds the reference (rare) and in finalize
+      float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+      float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+      ac.m_true0 = fmaxf(ac.m_true0, mx0);
+      ac.m_true1 = fmaxf(ac.m_true1, mx1);
+      if (__any_sync(kFullMask, (mx0 > ac.m_ref0) || (mx1 > ac.m_ref1))) {
 #pragma unroll
-    for (int off = 4; off <= 16; off <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, off));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, off));
-    }
-    ac.m_true0 = fmaxf(ac.m_true0, mx0);
-    ac.m_true1 = fmaxf(ac.m_true1, mx1);
-    if (__any_sync(kFullMask, (mx0 > ac.m_ref0) || (mx1 > ac.m_ref1))) {
-      const float n0 = (mx0 > ac.m_ref0) ? mx0 + kLazyTau : ac.m_ref0;
-      const float n1 = (mx1 > ac.m_ref1) ? mx1 + kLazyTau : ac.m_ref1;
-      const float alpha0 = ex2(ac.m_ref0 - n0);  // first tile: 2^(-inf) = 0; unchanged: 1
-      const float alpha1 = ex2(ac.m_ref1 - n1);
-      ac.m_ref0 = n0;
-      ac.m_ref1 = n1;
-      ac.l0 *= alpha0;
-      ac.l1 *= alpha1;
+        for (int off = 4; off <= 16; off <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, off));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, off));
+        }
+        const float n0 = (mx0 > ac.m_ref0) ? mx0 + kLazyTau : ac.m_ref0;
+        const float n1 = (mx1 > ac.m_ref1) ? mx1 + kLazyTau : ac.m_ref1;
+        const float alpha0 = ex2(ac.m_ref0 - n0);  // first tile: 2^(-inf) = 0; unchanged: 1
+        const float alpha1 = ex2(ac.m_ref1 - n1);
+        ac.m_ref0 = n0;
+        ac.m_ref1 = n1;
 #pragma unroll
-      for (int ch = 0; ch < NCH; ++ch) {
-        ac.acc[ch][0] *= alpha0;
-        ac.acc[ch][1] *= alpha1;
-        ac.acc[ch][2] *= alpha0;
-        ac.acc[ch][3] *= alpha1;
+        for (int ch = 0; ch < NCH; ++ch) {
+          ac.acc[ch][0] *= alpha0;
+          ac.acc[ch][1] *= alpha1;
+          ac.acc[ch][2] *= alpha0;
+          ac.acc[ch][3] *= alpha1;
+        }
+        ac.zacc[0] *= alpha0;
+        ac.zacc[1] *= alpha1;
+        ac.zacc[2] *= alpha0;
+        ac.zacc[3] *= alpha1;
       }
-      ac.zacc[0] *= alpha0;
-      ac.zacc[1] *= alpha1;
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        sc[mt][0] = ex2(sc[mt][0] - ac.m_ref0);
+        sc[mt][1] = ex2(sc[mt][1] - ac.m_ref1);
+        sc[mt][2] = ex2(sc[mt][2] - ac.m_ref0);
+        sc[mt][3] = ex2(sc[mt][3] - ac.m_ref1);
+      }
     }
+
+    // ---- output: O^T += V^T P^T ----
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
-      sc[mt][0] = ex2(sc[mt][0] - ac.m_ref0);
-      sc[mt][1] = ex2(sc[mt][1] - ac.m_ref1);
-      sc[mt][2] = ex2(sc[mt][2] - ac.m_ref0);
-      sc[mt][3] = ex2(sc[mt][3] - ac.m_ref1);
-      ac.l0 += sc[mt][0] + sc[mt][2];
-      ac.l1 += sc[mt][1] + sc[mt][3];
-    }
-  }
-
-  // ================= output: O^T += V^T P^T ========================================
-#pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
-    const uint32_t ph_lo = pack_half2(sc[mt][0], sc[mt][1]);  // token g,   heads 2t, 2t+1
-    const uint32_t ph_hi = pack_half2(sc[mt][2], sc[mt][3]);  // token g+8
-    {
-      // zero-point term: rows = groups, k = tokens; B = unscaled P^T
-      const uint32_t pz0 = movmatrix_trans(ph_lo);
-      const uint32_t pz1 = movmatrix_trans(ph_hi);
-      const __half* vz_t = vz_s + mt * 16 * NG;
-      uint32_t a0 = 0, a2 = 0;
-      if (g < NG) {
-        a0 = pack_half2(vz_t[(2 * t) * NG + g], vz_t[(2 * t + 1) * NG + g]);
-        a2 = pack_half2(vz_t[(2 * t + 8) * NG + g], vz_t[(2 * t + 9) * NG + g]);
+      const uint32_t ph_lo = pack_half2(sc[mt][0], sc[mt][1]);  // token g,   heads 2t, 2t+1
+      const uint32_t ph_hi = pack_half2(sc[mt][2], sc[mt][3]);  // token g+8
+      {
+        // zero-point term: rows = groups, k = tokens, B = unscaled P^T.  Lanes whose g is
+        // not a group re-read group g mod NG (those output rows are never used); row 8 is
+        // all ones on its k-slots and so accumulates sum_n p_n.
+        const uint32_t pz0 = movmatrix_trans(ph_lo);
+        const uint32_t pz1 = movmatrix_trans(ph_hi);
+        const uint32_t b = vz_a + mt * HALF;
+        const uint32_t a0 = lds_u16(b) | (lds_u16(b + NG * 2) << 16);
+        const uint32_t a2 = lds_u16(b + HALF / 2) | (lds_u16(b + HALF / 2 + NG * 2) << 16);
+        mma16816(ac.zacc, a0, qq.ones, a2, qq.ones, pz0, pz1);
       }
-      mma16816(ac.zacc, a0, 0u, a2, 0u, pz0, pz1);
-    }
-    uint32_t pb[NG][2];
-    {
-      const MetaRow<NG> s_lo = load_meta_row<NG>(vs_s + (mt * 16 + g) * NG);
-      const MetaRow<NG> s_hi = load_meta_row<NG>(vs_s + (mt * 16 + g + 8) * NG);
-      const __half2 p_lo = *reinterpret_cast<const __half2*>(&ph_lo);
-      const __half2 p_hi = *reinterpret_cast<const __half2*>(&ph_hi);
+      uint32_t pb[NG][2];
+      {
+        const MetaRow<NG> s_lo = lds_meta_row<NG>(vs_a + mt * HALF);
+        const MetaRow<NG> s_hi = lds_meta_row<NG>(vs_a + mt * HALF + HALF / 2);
+        const __half2 p_lo = *reinterpret_cast<const __half2*>(&ph_lo);
+        const __half2 p_hi = *reinterpret_cast<const __half2*>(&ph_hi);
 #pragma unroll
-      for (int grp = 0; grp < NG; ++grp) {
-        const __half2 a = __hmul2(p_lo, meta_bcast<NG>(s_lo, grp));
-        const __half2 bq = __hmul2(p_hi, meta_bcast<NG>(s_hi, grp));
-        pb[grp][0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&a));
-        pb[grp][1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&bq));
-      }
-    }
-#pragma unroll
-    for (int bb = 0; bb < NBLK; bb += 2) {
-      uint32_t r[4];
-      if constexpr (NBLK >= 2) {
-        ldmatrix_x4_trans(r, vc + qq.off[mt][bb >> 1]);
-      } else {
-        ldmatrix_x2_trans(r[0], r[1], vc + qq.off[mt][0]);
-        r[2] = r[3] = 0;
+        for (int grp = 0; grp < NG; ++grp) {
+          const __half2 a = __hmul2(p_lo, meta_bcast<NG>(s_lo, grp));
+          const __half2 bq = __hmul2(p_hi, meta_bcast<NG>(s_hi, grp));
+          pb[grp][0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&a));
+          pb[grp][1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&bq));
+        }
       }
 #pragma unroll
-      for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
-        const int blk = bb + jj;
-        const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
-        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+      for (int bb = 0; bb < NBLK; bb += 2) {
+        uint32_t r[4];
+        if constexpr (NBLK >= 2) {
+          ldmatrix_x4_trans(r, vc + qq.off[mt][bb >> 1]);
+        } else {
+          ldmatrix_x2_trans(r[0], r[1], vc + qq.off[mt][0]);
+          r[2] = r[3] = 0;
+        }
 #pragma unroll
-        for (int pp = 0; pp < P; ++pp) {
-          constexpr uint32_t M0 = C::MASK0;
-          const uint32_t mask = M0 << (NBITS * pp);
-          const int ch = pp * NBLK + blk;
-          const int grp = (16 * ch) / GS;
-          mma16816(ac.acc[ch], xl & mask, xl8 & mask, xh & mask, xh8 & mask, pb[grp][0],
-                   pb[grp][1]);
+        for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
+          const int blk = bb + jj;
+          const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
+          const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+#pragma unroll
+          for (int pp = 0; pp < P; ++pp) {
+            constexpr uint32_t M0 = C::MASK0;
+            const uint32_t mask = M0 << (NBITS * pp);
+            const int ch = pp * NBLK + blk;
+            const int grp = (16 * ch) / GS;
+            mma16816(ac.acc[ch], xl & mask, xl8 & mask, xh & mask, xh8 & mask, pb[grp][0],
+                     pb[grp][1]);
+          }
         }
       }
     }
-  }
+    (void)left;
+    (void)lane;
   }
 
   // Reduce the warp's state, convert it from the reference exponent to the true
@@ -477,12 +524,16 @@ struct FusedPolicy {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int off = 4; off <= 16; off <<= 1) {
-      ac.l0 += __shfl_xor_sync(kFullMask, ac.l0, off);
-      ac.l1 += __shfl_xor_sync(kFullMask, ac.l1, off);
+      ac.m_true0 = fmaxf(ac.m_true0, __shfl_xor_sync(kFullMask, ac.m_true0, off));
+      ac.m_true1 = fmaxf(ac.m_true1, __shfl_xor_sync(kFullMask, ac.m_true1, off));
     }
+    // row 8 of the zero-point accumulator (lanes 0-3, registers 2 and 3) holds sum_n p_n
+    const float l0 = __shfl_sync(kFullMask, ac.zacc[2], t);
+    const float l1 = __shfl_sync(kFullMask, ac.zacc[3], t);
     const float f0 = (ac.m_true0 == -INFINITY) ? 0.f : ex2(ac.m_ref0 - ac.m_true0);
     const float f1 = (ac.m_true1 == -INFINITY) ? 0.f : ex2(ac.m_ref1 - ac.m_true1);
-    st = SoftmaxState{ac.m_true0, ac.m_true1, ac.l0 * f0, ac.l1 * f1};
+    st = SoftmaxState{ac.m_true0, ac.m_true1, l0 * f0, l1 * f1};
+    const uint32_t vals_s = smem_u32(vals);
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch) {
       const int grp = (16 * ch) / GS;
@@ -491,10 +542,10 @@ struct FusedPolicy {
       const float z0 = __shfl_sync(kFullMask, ac.zacc[0], grp * 4 + t);
       const float z1 = __shfl_sync(kFullMask, ac.zacc[1], grp * 4 + t);
       // rows g / g+8 of the output tile are dims 16ch+2g / 16ch+2g+1
-      float2 h0 = make_float2(fmaf(ac.acc[ch][0], e, z0) * f0, fmaf(ac.acc[ch][2], e, z0) * f0);
-      float2 h1 = make_float2(fmaf(ac.acc[ch][1], e, z1) * f1, fmaf(ac.acc[ch][3], e, z1) * f1);
-      *reinterpret_cast<float2*>(&vals[(2 * t) * D + 16 * ch + 2 * g]) = h0;
-      *reinterpret_cast<float2*>(&vals[(2 * t + 1) * D + 16 * ch + 2 * g]) = h1;
+      sts_v2f(vals_s + ((2 * t) * D + 16 * ch + 2 * g) * 4, fmaf(ac.acc[ch][0], e, z0) * f0,
+              fmaf(ac.acc[ch][2], e, z0) * f0);
+      sts_v2f(vals_s + ((2 * t + 1) * D + 16 * ch + 2 * g) * 4, fmaf(ac.acc[ch][1], e, z1) * f1,
+              fmaf(ac.acc[ch][3], e, z1) * f1);
     }
   }
 };

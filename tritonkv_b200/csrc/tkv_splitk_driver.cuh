@@ -296,18 +296,21 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     }
   };
   cursor_skip_empty();
-  int issued = 0;
+  // Ring positions are kept as (slot, phase) and stepped with a compare, not derived
+  // from running counters: STAGES is 3, and a modulo per use was tens of instructions
+  // per tile.
+  int iss_slot = 0;  // slot the next issue fills
   bool need_proxy_fence = false;
   auto issue_next = [&]() {
     if (cur.cnt == 0) return;
-    const int slot = issued % STAGES;
+    const int slot = iss_slot;
+    iss_slot = (iss_slot + 1 == STAGES) ? 0 : iss_slot + 1;
     if (need_proxy_fence) {  // a generic-proxy epilogue touched the ring since the last issue
       fence_proxy_async();
       need_proxy_fence = false;
     }
     Policy::issue(p, maps, cur.row, min(kTok, cur.left), ring_u32 + slot * STAGE_BYTES,
                   ring + slot * STAGE_BYTES, bar_u32 + 8 * slot, lane);
-    ++issued;
     cur.row += WARPS * kTok;
     cur.left -= WARPS * kTok;
     --cur.cnt;
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   }
   int seg_k = 0;  // index of the current segment within this CTA
 
-  int consumed = 0;
+  int c_slot = 0, c_phase = 0;  // slot and barrier phase of the next tile to consume
   bool timed_out = false;
   typename Policy::Query qs;
   typename Policy::Accum acc;
@@ -336,40 +339,50 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     // Software pipeline: the scores of tile i+1 are computed in the same straight-line
     // block as the softmax/output update of tile i, so the two independent dependency
     // chains interleave in the instruction stream.
-    auto stage_u32 = [&](int k) { return ring_u32 + (k % STAGES) * STAGE_BYTES; };
-    auto stage_ptr = [&](int k) { return ring + (k % STAGES) * STAGE_BYTES; };
-    auto wait_tile = [&](int k) {
-      if (!mbar_wait_bounded(bar_u32 + 8 * (k % STAGES), (k / STAGES) & 1)) timed_out = true;
-    };
     if (my_tiles > 0 && !timed_out) {
       typename Policy::Scores sc_cur;
-      wait_tile(consumed);
+      if (!mbar_wait_bounded(bar_u32 + 8 * c_slot, c_phase)) timed_out = true;
       __syncwarp();
       if (!timed_out)
-        Policy::scores(sc_cur, qs, stage_u32(consumed), stage_ptr(consumed), left, p.qk_scale, lane);
-      for (int i = 0; i + 1 < my_tiles && !timed_out; ++i) {
-        wait_tile(consumed + 1);
-        if (timed_out) break;
+        Policy::scores(sc_cur, qs, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES, left,
+                       p.qk_scale, lane);
+      for (int i = 1; i < my_tiles && !timed_out; ++i) {
+        int n_slot = c_slot + 1, n_phase = c_phase;
+        if (n_slot == STAGES) {
+          n_slot = 0;
+          n_phase ^= 1;
+        }
+        if (!mbar_wait_bounded(bar_u32 + 8 * n_slot, n_phase)) {
+          timed_out = true;
+          break;
+        }
         __syncwarp();
         issue_next();  // refills the stage whose tile was finished in the previous iteration
         typename Policy::Scores sc_next;
-        Policy::scores(sc_next, qs, stage_u32(consumed + 1), stage_ptr(consumed + 1),
+        Policy::scores(sc_next, qs, ring_u32 + n_slot * STAGE_BYTES, ring + n_slot * STAGE_BYTES,
                        left - WARPS * kTok, p.qk_scale, lane);
-        Policy::update(acc, qs, sc_cur, stage_u32(consumed), stage_ptr(consumed), left, lane);
+        Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
+                       left, lane);
         sc_cur = sc_next;
         left -= WARPS * kTok;
-        ++consumed;
+        c_slot = n_slot;
+        c_phase = n_phase;
       }
       if (!timed_out) {
         __syncwarp();
         issue_next();
-        Policy::update(acc, qs, sc_cur, stage_u32(consumed), stage_ptr(consumed), left, lane);
-        ++consumed;
+        Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
+                       left, lane);
+        if (++c_slot == STAGES) {
+          c_slot = 0;
+          c_phase ^= 1;
+        }
       }
     }
 
     // ---- segment epilogue: merge the warps, store the partial ----
-    float* vals = reinterpret_cast<float*>(ring + ((consumed + STAGES - 1) % STAGES) * STAGE_BYTES);
+    const int vals_slot = (c_slot == 0 ? STAGES : c_slot) - 1;  // the stage consumed last
+    float* vals = reinterpret_cast<float*>(ring + vals_slot * STAGE_BYTES);
     SoftmaxState st;
     if (my_tiles > 0) {
       Policy::finalize(acc, vals, st, lane);  // the stage consumed last is free until the next issue
@@ -383,7 +396,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
       s_l[warp][2 * t] = st.l0;
       s_l[warp][2 * t + 1] = st.l1;
     }
-    if (lane == 0) s_slot[warp] = (consumed + STAGES - 1) % STAGES;
+    if (lane == 0) s_slot[warp] = vals_slot;
     __syncthreads();
     // Each thread merges float4 columns; per item the four warps' loads are independent
     // (no data-dependent branch around them), so they overlap instead of serialising.
