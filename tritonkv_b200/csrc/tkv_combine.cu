@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(kCombineThreads)
   __shared__ float red_m[8];
   __shared__ float4 red_a[8][8];
   __shared__ float red_l[8];
+  __shared__ float sh_m[kCombineThreads];
+  __shared__ float sh_l[kCombineThreads];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = blockIdx.x;            // b*HQ + h
   const int d0 = blockIdx.y * kCombineSlice;
@@ -41,24 +43,22 @@ __global__ void __launch_bounds__(kCombineThreads)
   float L = 0.f;
   float M;
   if (NS <= 32 * kCached) {
-    // All loads are issued back to back, before any of them is used and before the
-    // block-wide maximum is known: one round trip to L2 instead of one per slot.  Slots
-    // past NS re-read the last slot (always in bounds) and are discarded.
-    float ms[kCached], ls[kCached];
+    // One round trip: every load is issued before any value is used.  The acc rows go
+    // straight to registers; (m, l) of slot `tid` are fetched once per CTA and shared
+    // through shared memory instead of 16 scalar loads per thread.  Loads bypass L1
+    // (each value is read once; measured 0.2 us faster than the read-only path).
     float4 xs[kCached];
 #pragma unroll
     for (int i = 0; i < kCached; ++i) {
-      const int s = min(sg + 32 * i, NS - 1);
-      ms[i] = __ldg(mrow + s * ml_slot);
-      ls[i] = __ldg(lrow + s * ml_slot);
-      xs[i] = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
+      const int s = min(sg + 32 * i, NS - 1);  // slots past NS re-read the last one, unused
+      xs[i] = __ldcg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
     }
-    float mloc = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < kCached; ++i) {
-      if (sg + 32 * i >= NS) ms[i] = -INFINITY;
-      mloc = fmaxf(mloc, ms[i]);
-    }
+    const int sm = min(tid, NS - 1);
+    float mloc = __ldcg(mrow + sm * ml_slot);
+    const float lmine = __ldcg(lrow + sm * ml_slot);
+    if (tid >= NS) mloc = -INFINITY;
+    sh_m[tid] = mloc;
+    sh_l[tid] = lmine;
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1)
       mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
@@ -69,18 +69,19 @@ __global__ void __launch_bounds__(kCombineThreads)
     for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
 #pragma unroll
     for (int i = 0; i < kCached; ++i) {
-      if (ms[i] > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never use it
-        const float w = ex2(ms[i] - M);
+      const float ms = sh_m[sg + 32 * i];  // -inf past NS and for empty slots
+      if (ms > -INFINITY) {  // empty slots (m = -inf) may hold anything in acc: never use it
+        const float w = ex2(ms - M);
         a.x = fmaf(w, xs[i].x, a.x);
         a.y = fmaf(w, xs[i].y, a.y);
         a.z = fmaf(w, xs[i].z, a.z);
         a.w = fmaf(w, xs[i].w, a.w);
-        L = fmaf(w, ls[i], L);
+        L = fmaf(w, sh_l[sg + 32 * i], L);
       }
     }
   } else {
     float mloc = -INFINITY;
-    for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldg(mrow + s * ml_slot));
+    for (int s = tid; s < NS; s += kCombineThreads) mloc = fmaxf(mloc, __ldcg(mrow + s * ml_slot));
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1)
       mloc = fmaxf(mloc, __shfl_xor_sync(kFullMask, mloc, off));
@@ -91,15 +92,15 @@ __global__ void __launch_bounds__(kCombineThreads)
     for (int w = 1; w < 8; ++w) M = fmaxf(M, red_m[w]);
 #pragma unroll 4
     for (int s = sg; s < NS; s += 32) {
-      const float ms = __ldg(mrow + s * ml_slot);
+      const float ms = __ldcg(mrow + s * ml_slot);
       if (ms > -INFINITY) {
         const float w = ex2(ms - M);
-        const float4 x = __ldg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(arow + (int64_t)s * a_slot));
         a.x = fmaf(w, x.x, a.x);
         a.y = fmaf(w, x.y, a.y);
         a.z = fmaf(w, x.z, a.z);
         a.w = fmaf(w, x.w, a.w);
-        L = fmaf(w, __ldg(lrow + s * ml_slot), L);
+        L = fmaf(w, __ldcg(lrow + s * ml_slot), L);
       }
     }
   }
@@ -147,6 +148,7 @@ __global__ void __launch_bounds__(kCombineThreads)
 constexpr int kSmallWarps = 8;
 constexpr int kSmallMaxNS = 16;
 
+template <int kMaxNS>  // compile-time bound on the slots, so no load is issued for nothing
 __global__ void __launch_bounds__(kSmallWarps * 32)
     combine_small_kernel(const float* __restrict__ acc, const float* __restrict__ m,
                          const float* __restrict__ l, float* __restrict__ out,
@@ -160,36 +162,36 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
   // loads first, uses afterwards: one round trip for (m, l), one for the acc rows
-  float ms[kSmallMaxNS], ls[kSmallMaxNS];
+  float ms[kMaxNS], ls[kMaxNS];
 #pragma unroll
-  for (int s = 0; s < kSmallMaxNS; ++s) {
+  for (int s = 0; s < kMaxNS; ++s) {
     const int sc = min(s, NS - 1);
-    ms[s] = __ldg(mrow + sc * ml_slot);
-    ls[s] = __ldg(lrow + sc * ml_slot);
+    ms[s] = __ldcg(mrow + sc * ml_slot);
+    ls[s] = __ldcg(lrow + sc * ml_slot);
   }
   float M = -INFINITY;
 #pragma unroll
-  for (int s = 0; s < kSmallMaxNS; ++s) {
+  for (int s = 0; s < kMaxNS; ++s) {
     if (s >= NS) ms[s] = -INFINITY;
     M = fmaxf(M, ms[s]);
   }
   float L = 0.f;
 #pragma unroll
-  for (int s = 0; s < kSmallMaxNS; ++s) {
+  for (int s = 0; s < kMaxNS; ++s) {
     ms[s] = (ms[s] > -INFINITY) ? ex2(ms[s] - M) : 0.f;  // weight of slot s
     if (ms[s] > 0.f) L = fmaf(ms[s], ls[s], L);
   }
   const float inv = (out_m == nullptr) ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
   for (int v = lane; v < (D >> 2); v += 32) {
-    float4 x[kSmallMaxNS];
+    float4 x[kMaxNS];
 #pragma unroll
-    for (int s = 0; s < kSmallMaxNS; ++s) {
+    for (int s = 0; s < kMaxNS; ++s) {
       const int sc = min(s, NS - 1);
-      x[s] = __ldg(reinterpret_cast<const float4*>(acc + (int64_t)row * a_row + sc * a_slot) + v);
+      x[s] = __ldcg(reinterpret_cast<const float4*>(acc + (int64_t)row * a_row + sc * a_slot) + v);
     }
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int s = 0; s < kSmallMaxNS; ++s) {
+    for (int s = 0; s < kMaxNS; ++s) {
       if (s < NS && ms[s] > 0.f) {  // empty slots may hold anything in acc: never use it
         a.x = fmaf(ms[s], x[s].x, a.x);
         a.y = fmaf(ms[s], x[s].y, a.y);
@@ -227,9 +229,20 @@ extern "C" int tkv_combine_strided(const float* acc, const float* m, const float
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
   if (NS <= kSmallMaxNS && rows >= 256) {
     const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
-    TKV_CUDA(launch_pdl(tkv::combine_small_kernel, dim3(blocks), dim3(kSmallWarps * 32), 0,
-                        (cudaStream_t)stream, acc, m, l, out, out_m, out_l, (int)rows, NS, D,
-                        acc_row_stride, acc_slot_stride, ml_row_stride, ml_slot_stride));
+#define TKV_SMALL(N)                                                                          \
+  TKV_CUDA(launch_pdl(tkv::combine_small_kernel<N>, dim3(blocks), dim3(kSmallWarps * 32), 0,   \
+                      (cudaStream_t)stream, acc, m, l, out, out_m, out_l, (int)rows, NS, D,    \
+                      acc_row_stride, acc_slot_stride, ml_row_stride, ml_slot_stride))
+    if (NS <= 2) {
+      TKV_SMALL(2);
+    } else if (NS <= 4) {
+      TKV_SMALL(4);
+    } else if (NS <= 8) {
+      TKV_SMALL(8);
+    } else {
+      TKV_SMALL(16);
+    }
+#undef TKV_SMALL
     return TKV_OK;
   }
   dim3 grid((unsigned)rows, D / kCombineSlice);

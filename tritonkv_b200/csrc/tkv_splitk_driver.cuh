@@ -74,13 +74,16 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
     // Few, long units (small batches): give every unit its own whole number of CTAs, so
     // that no CTA straddles two units and pays a second query load and epilogue.  Taken
     // when it lengthens the longest CTA by at most one tile.
+    // CTA j of a unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG): every resident slot of
+    // the device is used and tile counts differ by at most one.
     if (units * 2 <= wave) {
       const int cpu = (int)(wave / units);
-      const int TCu = (s.TUf + cpu - 1) / cpu;
+      const int SEGu = s.TUf < cpu ? s.TUf : cpu;
+      const int TCu = (s.TUf + SEGu - 1) / SEGu;
       if (TCu <= s.TC + 1) {
         s.persistent = 2;
         s.TC = TCu;
-        s.SEG = (s.TUf + TCu - 1) / TCu;
+        s.SEG = SEGu;
         s.grid = (int)(units * s.SEG);
       }
     }
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     if (g0 >= g1) return;
     seg = segment_at<kTok>(p, sc, g0, g1, cta);
   } else if (sc.persistent == 2) {
-    // unit-aligned: CTA j of the unit's SEG takes tiles [j*TC, (j+1)*TC) of the unit
+    // unit-aligned: CTA j of the unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG) of the unit
     const int u = cta / sc.SEG, j = cta - u * sc.SEG;
     const int bh = u / sc.NS;
     seg.split = u - bh * sc.NS;
@@ -224,11 +227,11 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     seg.hkv = hk / p.hchunks;
     seg.hc = hk - seg.hkv * p.hchunks;
     const int TU = (seg.split == sc.NS - 1) ? sc.TUl : sc.TUf;
-    const int t0 = j * sc.TC;
+    const int t0 = (int)(((int64_t)j * TU) / sc.SEG);
     const int lo_unit = seg.split * p.split_size;
     seg.hi = min(lo_unit + p.split_size, p.S);
     seg.lo_tok = lo_unit + t0 * kTok;
-    seg.ntiles = min(sc.TC, TU - t0);
+    seg.ntiles = (int)(((int64_t)(j + 1) * TU) / sc.SEG) - t0;
     seg.slot = seg.split * sc.SEG + j;
     seg.fill_from = seg.fill_to = -1;
     g0 = 0;
