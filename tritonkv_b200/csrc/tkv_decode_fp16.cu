@@ -56,12 +56,14 @@ struct Fp16Policy {
   // Fill one stage with the 16 tokens starting at global row `row`: 16-byte cp.async per
   // lane into the 128B-swizzled layout (rows past the unit end are zero-filled), then one
   // arrival per lane on the stage barrier that fires when the lane's copies have landed.
-  __device__ static __forceinline__ void issue(const DecodeParams& p, const Maps& maps, int64_t row,
-                                               int nvalid, uint32_t st, uint8_t* st_ptr,
-                                               uint32_t bar, int lane) {
+  struct IssueState {};
+  __device__ static __forceinline__ void issue_init(IssueState&, const DecodeParams&, int) {}
+  __device__ static __forceinline__ void issue(const IssueState&, const DecodeParams& p,
+                                               const Maps& maps, int row, int nvalid, uint32_t st,
+                                               uint8_t* st_ptr, uint32_t bar, int lane) {
     constexpr int NCC = TOK * (ROW / 16);  // 16-byte chunks per tile
-    const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(p.k) + row * ROW;
-    const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.v) + row * ROW;
+    const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(p.k) + (int64_t)row * ROW;
+    const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.v) + (int64_t)row * ROW;
 #pragma unroll
     for (int i0 = 0; i0 < NCC; i0 += 32) {
       const int i = i0 + lane;
@@ -77,8 +79,12 @@ struct Fp16Policy {
 
   // query fragments: B operand, k-slots (2t,2t+1) <-> dims 16c+2t, 16c+2t+1 and
   // (2t+8, 2t+9) <-> dims 16c+8+2t, 16c+9+2t, column g = head g.
+  static constexpr int QFRAG_BYTES = 0;  // every warp reads the query rows itself
+  __device__ static __forceinline__ void lane_init(Query&, const DecodeParams&, int) {}
+  __device__ static __forceinline__ void build_query(const DecodeParams&, const uint8_t*, uint32_t,
+                                                     int, int) {}
   __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p,
-                                                    const uint8_t* qsm, int lane) {
+                                                    const uint8_t* qsm, uint32_t, int lane) {
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* qrow = qsm + g * D * (p.q_dtype == TKV_DTYPE_F32 ? 4 : 2);
 #pragma unroll

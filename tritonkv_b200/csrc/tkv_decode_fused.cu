@@ -164,15 +164,32 @@ struct FusedPolicy {
     prefetch_tensormap(&maps.v);
   }
 
+  // Per-lane constants of the copy path, set once per warp.
+  static constexpr int CPA = C::META_BYTES / 16;                   // 16-byte chunks per metadata array
+  static constexpr int ROUNDS = (4 * CPA + 31) / 32;               // cp.async rounds per tile
+  struct IssueState {
+    const uint8_t* src[ROUNDS];  // this lane's source of round r at global row 0
+  };
+  __device__ static __forceinline__ void issue_init(IssueState& is, const DecodeParams& p, int lane) {
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+      const int i = r * 32 + lane;              // chunk index over (ks | kz | vs | vz)
+      const int arr = (i / CPA) & 3, c = i % CPA;
+      const __half* base = arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz;
+      is.src[r] = reinterpret_cast<const uint8_t*>(base) + c * 16;
+    }
+  }
+
   // Fill one stage with the 32 tokens starting at global row `row`; `nvalid` of them
   // belong to the unit.
-  __device__ static __forceinline__ void issue(const DecodeParams& p, const Maps& maps, int64_t row,
-                                               int nvalid, uint32_t st, uint8_t* st_ptr,
-                                               uint32_t bar, int lane) {
+  __device__ static __forceinline__ void issue(const IssueState& is, const DecodeParams& p,
+                                               const Maps& maps, int row, int nvalid, uint32_t st,
+                                               uint8_t* st_ptr, uint32_t bar, int lane) {
     if (lane == 0) {
       mbar_arrive_expect_tx(bar, 2 * kTok * DP);
       // wide view: the tensor is [bytes/128, 128]; narrow view: [tokens, DP]
-      const int c1 = p.wide ? (int)((row * DP) >> 7) : (int)row;
+      constexpr int SH = (DP == 64) ? 1 : (DP == 32) ? 2 : 3;  // row*DP/128 = row >> SH
+      const int c1 = p.wide ? (row >> SH) : row;
       tma_load_2d(st, &maps.k, 0, c1, bar);
       tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
     }
@@ -181,22 +198,17 @@ struct FusedPolicy {
     // then posts one arrival on the stage barrier that fires when its copies have landed.
     const uint32_t mst = st + 2 * C::CODE_BYTES;
     if (p.meta_aligned && nvalid == kTok) {
-      constexpr int CPA = C::META_BYTES / 16;  // 16-byte chunks per metadata array
-      const int64_t off = row * NG;            // halves
+      const int64_t off = (int64_t)row * (NG * 2);  // bytes
 #pragma unroll
-      for (int i0 = 0; i0 < 4 * CPA; i0 += 32) {
-        const int i = i0 + lane;
-        if (4 * CPA >= 32 || i < 4 * CPA) {
-          const int arr = i / CPA, c = i - arr * CPA;
-          const __half* base = arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz;
-          cp_async16(mst + i * 16, reinterpret_cast<const uint8_t*>(base + off) + c * 16, 16);
-        }
+      for (int r = 0; r < ROUNDS; ++r) {
+        if (4 * CPA >= 32 || lane < 4 * CPA)
+          cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + off, 16);
       }
       cp_async_mbar_arrive_noinc(bar);
     } else {
       // ragged tail or unaligned rows: plain loads; tokens past the end get scale = zero = 0
       __half* dstm = reinterpret_cast<__half*>(st_ptr + 2 * C::CODE_BYTES);
-      const int64_t off = row * NG;
+      const int64_t off = (int64_t)row * NG;
       const __half zero = __float2half(0.f);
       for (int i = lane; i < kTok * NG; i += 32) {
         const bool ok = (i / NG) < nvalid;
@@ -209,43 +221,51 @@ struct FusedPolicy {
     }
   }
 
-  // `qsm`: the segment's 8 query rows (raw dtype, zero rows for heads past the group)
-  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p,
-                                                    const uint8_t* qsm, int lane) {
+  // Lane constants of the tile loop: set once per warp.
+  __device__ static __forceinline__ void lane_init(Query& qq, const DecodeParams& p, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    {
-      // ldmatrix addressing: lane l supplies the row address of matrix l/8, row l%8;
-      // matrices are (tokens 0-7, blk), (tokens 8-15, blk), (tokens 0-7, blk+1), (tokens 8-15, blk+1).
-      const int lm_r = (lane & 7) + ((lane >> 3) & 1) * 8;
-      const int lm_b = (NBLK >= 2) ? (lane >> 4) : 0;
+    // ldmatrix addressing: lane l supplies the row address of matrix l/8, row l%8;
+    // matrices are (tokens 0-7, blk), (tokens 8-15, blk), (tokens 0-7, blk+1), (tokens 8-15, blk+1).
+    const int lm_r = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int lm_b = (NBLK >= 2) ? (lane >> 4) : 0;
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int pr = 0; pr < C::NPAIR; ++pr) {
-          const int n = 16 * mt + lm_r, blk = 2 * pr + lm_b;
-          const int L = n * NBLK + blk;  // linear 16-byte chunk index inside the tile
-          int Ls;
-          if (p.wide) {
-            Ls = (L & ~7) | ((L ^ (L >> 3)) & 7);                       // 128B swizzle
-          } else {
-            const int swz = (NBLK > 1) ? ((n >> C::SWZ_SHIFT) & (NBLK - 1)) : 0;
-            Ls = n * NBLK + (blk ^ swz);                                // 32B / 64B swizzle
-          }
-          qq.off[mt][pr] = Ls << 4;
+      for (int pr = 0; pr < C::NPAIR; ++pr) {
+        const int n = 16 * mt + lm_r, blk = 2 * pr + lm_b;
+        const int L = n * NBLK + blk;  // linear 16-byte chunk index inside the tile
+        int Ls;
+        if (p.wide) {
+          Ls = (L & ~7) | ((L ^ (L >> 3)) & 7);                       // 128B swizzle
+        } else {
+          const int swz = (NBLK > 1) ? ((n >> C::SWZ_SHIFT) & (NBLK - 1)) : 0;
+          Ls = n * NBLK + (blk ^ swz);                                // 32B / 64B swizzle
         }
-    }
+        qq.off[mt][pr] = Ls << 4;
+      }
     qq.o_row = g * NG * 2;
     qq.o_kz = (NG >= 2) ? (g * NG + ((2 * t) % NG)) * 2 : g * 2;
     qq.o_vz = ((2 * t) * NG + (g % NG)) * 2;
     qq.ones = (lane < 4) ? 0x3C003C00u : 0u;
+  }
 
+  // Query fragments of a segment are the same for the four warps: each warp builds the
+  // chunks w, w+WARPS, ... and the per-chunk sums of q, the CTA synchronises, and every
+  // warp reads the finished fragments (layout [word quad][lane], conflict free).
+  static constexpr int QFRAG_WORDS = NCH * 2;                        // per lane
+  static constexpr int QFRAG_BYTES = 32 * QFRAG_WORDS * 4 + NCH * 8 * 4;  // fragments + chunk sums
+  static_assert(QFRAG_WORDS % 4 == 0, "fragments are read as 128-bit words");
+
+  // `qsm`: the segment's 8 query rows (raw dtype, zero rows for heads past the group)
+  __device__ static __forceinline__ void build_query(const DecodeParams& p, const uint8_t* qsm,
+                                                     uint32_t qfrag, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
     const uint8_t* qrow = qsm + g * D * (p.q_dtype == TKV_DTYPE_F32 ? 4 : 2);
     const uint32_t qrow_s = smem_u32(qrow);
-    float gsum[NG];
 #pragma unroll
-    for (int i = 0; i < NG; ++i) gsum[i] = 0.f;
-#pragma unroll
-    for (int ch = 0; ch < NCH; ++ch) {
+    for (int c0 = 0; c0 < NCH; c0 += WARPS) {
+      const int ch = c0 + warp;
+      if (NCH % WARPS != 0 && ch >= NCH) break;
       __half x[4];
       if (p.q_dtype == TKV_DTYPE_F16) {
         const uint2 v = lds_v2(qrow_s + (16 * ch + 4 * t) * 2);
@@ -258,40 +278,62 @@ struct FusedPolicy {
       // query down by the same power of two (exact unless |q| < 2^-14 2^(NBITS p), where the
       // absolute error stays below 2^-25) lets every slice share one accumulator and scale.
       const int slice = ch / NBLK;
-      const __half2 down = __float2half2_rn(pow2i(-NBITS * slice));
+      const __half2 down = __float2half2_rn(ex2((float)(-NBITS * slice)));
       const uint32_t u0 = pack_half2(x[0], x[2]);  // k-slots 2t, 2t+1   <-> dims 16ch+4t, 16ch+4t+2
       const uint32_t u1 = pack_half2(x[1], x[3]);  // k-slots 2t+8, 2t+9 <-> dims 16ch+4t+1, 16ch+4t+3
       const __half2 v0 = __hmul2(*reinterpret_cast<const __half2*>(&u0), down);
       const __half2 v1 = __hmul2(*reinterpret_cast<const __half2*>(&u1), down);
-      qq.qf[ch][0] = *reinterpret_cast<const uint32_t*>(&v0);
-      qq.qf[ch][1] = *reinterpret_cast<const uint32_t*>(&v1);
-      gsum[(16 * ch) / GS] += (__half2float(x[0]) + __half2float(x[1])) +
-                              (__half2float(x[2]) + __half2float(x[3]));
+      float sum = (__half2float(x[0]) + __half2float(x[1])) + (__half2float(x[2]) + __half2float(x[3]));
+      sum += __shfl_xor_sync(kFullMask, sum, 1);
+      sum += __shfl_xor_sync(kFullMask, sum, 2);
+      // words (2ch, 2ch+1) of this lane: quad ch/2, position 2(ch%2)
+      const uint32_t dst = qfrag + (ch >> 1) * 512 + lane * 16 + (ch & 1) * 8;
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(dst),
+                   "r"(*reinterpret_cast<const uint32_t*>(&v0)),
+                   "r"(*reinterpret_cast<const uint32_t*>(&v1))
+                   : "memory");
+      if (t == 0)
+        asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(qfrag + 32 * QFRAG_WORDS * 4 + (ch * 8 + g) * 4),
+                     "f"(sum)
+                     : "memory");
     }
+  }
+
+  // After the CTA barrier that follows build_query.
+  __device__ static __forceinline__ void load_query(Query& qq, const DecodeParams& p,
+                                                    const uint8_t*, uint32_t qfrag, int lane) {
+    const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int i = 0; i < NG; ++i) {
-      gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 1);
-      gsum[i] += __shfl_xor_sync(kFullMask, gsum[i], 2);
+    for (int q4 = 0; q4 < QFRAG_WORDS / 4; ++q4) {
+      const uint4 v = lds_v4(qfrag + q4 * 512 + lane * 16);
+      qq.qf[2 * q4][0] = v.x;
+      qq.qf[2 * q4][1] = v.y;
+      qq.qf[2 * q4 + 1][0] = v.z;
+      qq.qf[2 * q4 + 1][1] = v.w;
     }
-    // k-slots 2t, 2t+1 carry the f16 high parts of qk_scale * qsum of groups 2t, 2t+1,
-    // k-slots 2t+8, 2t+9 the low parts (the zero-point words are fed to both halves).
-    __half hi0 = __float2half(0.f), hi1 = hi0, lo0 = hi0, lo1 = hi0;
+    // k-slots 2t, 2t+1 carry the f16 high parts of qk_scale * (sum of q over groups 2t, 2t+1)
+    // for head g, k-slots 2t+8, 2t+9 the low parts (the zero-point words feed both halves).
+    constexpr int CPG = GS / 16;  // chunks per group
+    const uint32_t sums = qfrag + 32 * QFRAG_WORDS * 4 + g * 4;
+    __half hi[2], lo[2];
 #pragma unroll
-    for (int i = 0; i < NG; ++i) {
-      const float v = gsum[i] * p.qk_scale;
-      const __half hi16 = __float2half_rn(v);
-      const __half lo16 = __float2half_rn(v - __half2float(hi16));
-      if (i == 2 * t) {
-        hi0 = hi16;
-        lo0 = lo16;
+    for (int k = 0; k < 2; ++k) {
+      const int grp = 2 * t + k;
+      float v = 0.f;
+      if (grp < NG) {
+#pragma unroll
+        for (int c = 0; c < CPG; ++c) {
+          float x;
+          asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(x) : "r"(sums + ((grp * CPG + c) * 8) * 4));
+          v += x;
+        }
       }
-      if (i == 2 * t + 1) {
-        hi1 = hi16;
-        lo1 = lo16;
-      }
+      v *= p.qk_scale;
+      hi[k] = __float2half_rn(v);
+      lo[k] = __float2half_rn(v - __half2float(hi[k]));
     }
-    qq.qz0 = pack_half2(hi0, hi1);
-    qq.qz1 = pack_half2(lo0, lo1);
+    qq.qz0 = pack_half2(hi[0], hi[1]);
+    qq.qz1 = pack_half2(lo[0], lo[1]);
   }
 
   __device__ static __forceinline__ void reset(Accum& ac) {

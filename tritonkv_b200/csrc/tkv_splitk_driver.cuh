@@ -142,7 +142,7 @@ __device__ __forceinline__ Segment segment_at(const DecodeParams& p, const Split
 // Per-warp cursor over the tiles this warp will issue, possibly segments ahead.
 struct IssueCursor {
   int seg_g;      // global tile index where the cursor's segment starts (persistent mode)
-  int64_t row;    // global row (token index over the whole cache tensor) of the next tile
+  int row;        // global row (token index over the whole cache tensor, < 2^31) of the next tile
   int left;       // tokens from the next tile's first token to the end of its unit
   int cnt;        // tiles this warp still has to issue in the cursor's segment
   int g_end;      // end of the cursor's segment
@@ -185,6 +185,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   const uint32_t qbar_u32 = smem_u32(qbars);
   uint8_t* qbuf = reinterpret_cast<uint8_t*>(qbars + 2);
   const uint32_t qbuf_u32 = smem_u32(qbuf);
+  const uint32_t qfrag_u32 = qbuf_u32 + 2 * QB;  // query fragments shared by the warps
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + 8 * s, Policy::BAR_COUNT);
@@ -272,12 +273,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   }
 
   __syncthreads();  // barriers initialised
-  // Launched as a programmatic dependent: everything above ran while the previous kernel
-  // of the stream was finishing; global memory is touched only from here on.
-  pdl_wait();
-  // The query rows go first: behind the first tiles of every warp of the grid they would
-  // queue for microseconds, ahead of them they arrive while the tiles are being issued.
-  prefetch_q(0, seg.b, seg.hkv, seg.hc);
 
   // ---- issue cursor ----
   auto cursor_enter = [&](IssueCursor& c, const Segment& s, int seg_g) {
@@ -285,9 +280,11 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     c.g_end = s.g_end;
     c.cnt = s.ntiles > warp ? (s.ntiles - warp + WARPS - 1) / WARPS : 0;
     const int tok = s.lo_tok + warp * kTok;
-    c.row = ((int64_t)s.b * p.HKV + s.hkv) * p.S + tok;
+    c.row = (s.b * p.HKV + s.hkv) * p.S + tok;
     c.left = s.hi - tok;
   };
+  typename Policy::IssueState ist;
+  Policy::issue_init(ist, p, lane);
   IssueCursor cur;
   cursor_enter(cur, seg, g0);
   auto cursor_skip_empty = [&]() {
@@ -312,13 +309,21 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
       fence_proxy_async();
       need_proxy_fence = false;
     }
-    Policy::issue(p, maps, cur.row, min(kTok, cur.left), ring_u32 + slot * STAGE_BYTES,
+    Policy::issue(ist, p, maps, cur.row, min(kTok, cur.left), ring_u32 + slot * STAGE_BYTES,
                   ring + slot * STAGE_BYTES, bar_u32 + 8 * slot, lane);
     cur.row += WARPS * kTok;
     cur.left -= WARPS * kTok;
     --cur.cnt;
     cursor_skip_empty();
   };
+  typename Policy::Query qs;
+  Policy::lane_init(qs, p, lane);
+  // Launched as a programmatic dependent: everything above ran while the previous kernel
+  // of the stream was finishing; global memory is touched only from here on.
+  pdl_wait();
+  // The query rows go first: behind the first tiles of every warp of the grid they would
+  // queue for microseconds, ahead of them they arrive while the tiles are being issued.
+  prefetch_q(0, seg.b, seg.hkv, seg.hc);
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue_next();
   if (sc.persistent == 1 && seg.g_end < g1) {
@@ -329,13 +334,16 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
 
   int c_slot = 0, c_phase = 0;  // slot and barrier phase of the next tile to consume
   bool timed_out = false;
-  typename Policy::Query qs;
   typename Policy::Accum acc;
 
   for (int g = g0;;) {
     // ---- one segment ----
     if (!mbar_wait_bounded(qbar_u32 + 8 * (seg_k & 1), (seg_k >> 1) & 1)) timed_out = true;
-    Policy::load_query(qs, p, qbuf + (seg_k & 1) * QB, lane);
+    if (Policy::QFRAG_BYTES > 0) {
+      Policy::build_query(p, qbuf + (seg_k & 1) * QB, qfrag_u32, warp, lane);
+      __syncthreads();
+    }
+    Policy::load_query(qs, p, qbuf + (seg_k & 1) * QB, qfrag_u32, lane);
     Policy::reset(acc);
     const int my_tiles = seg.ntiles > warp ? (seg.ntiles - warp + WARPS - 1) / WARPS : 0;
     int left = seg.hi - (seg.lo_tok + warp * kTok);
@@ -527,6 +535,7 @@ struct SplitLaunch {
   static int smem_bytes() {
     return Policy::WARPS * Policy::STAGES * Policy::STAGE_BYTES + Policy::WARPS * Policy::STAGES * 8 +
            16 + 2 * kHeadsPerCta * Policy::D * 4 +  // query barriers and the two query slots
+           Policy::QFRAG_BYTES +                    // query fragments shared by the warps
            1024;                                    // slack for the 1024-byte alignment of the ring
   }
   static const void* fn() { return reinterpret_cast<const void*>(&splitk_kernel<Policy>); }
