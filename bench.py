@@ -47,11 +47,11 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the split kernel from the
 # ncu capture summarised under profiles/ (None until a capture for that cell exists).
 NCU_TRAFFIC_BYTES = {
-    # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.04 MB read + 0 written
-    "qwen-b1/4b/ctx65536": 21_043_200,
-    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.09 MB read + 3.0 MB written) at batch 16,
-    # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.3 %)
-    "llama8b-b64/4b/ctx4096": 4 * (84_087_040 + 2_990_000),
+    # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.05 MB read + 0 written
+    "qwen-b1/4b/ctx65536": 21_047_040,
+    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.10 MB read + 3.6 MB written) at batch 16,
+    # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.4 %)
+    "llama8b-b64/4b/ctx4096": 4 * (84_095_104 + 3_620_608),
 }
 
 
@@ -324,7 +324,11 @@ def run_ours(args):
         if not history_split:
             sg = harness.StepGraphs(steps, K)
         wg = harness.StepGraphs(steps, W) if W != K else sg
-        wg.run()
+        # The timed graphs are replayed once before the W warm-up steps: the first launch
+        # of an instantiated graph uploads it to the device (about 0.75 us per step for
+        # these thousand-node graphs), which is set-up cost, not step time.
+        sg.run()
+        wg.run()  # the W warm-up steps
         torch.cuda.synchronize()
         ms = harness.time_region(sg.run, barrier)
     else:
@@ -420,6 +424,7 @@ def run_ours(args):
                 "partition": ("history split over ranks + NCCL all-gather of (acc,m,l) + combine"
                               if history_split else "independent sequences per rank, no collective"),
                 "partial_slots_per_head": (ws.get("key") or (0, 0, 1, 0))[2],
+                "untimed_steps_before_timing": K + W if graphs else 3 * R + W,
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * K, "clocks": clocks, "parity_vs_oracle": parity,
