@@ -430,9 +430,20 @@ def run_ours(args):
             "gpu_launches": launches_per_step * K, "clocks": clocks, "parity_vs_oracle": parity,
             "rows": rows,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
+        # Tear down in order: graphs that hold captured NCCL kernels go first, then the
+        # group.  A watchdog ends the process if the teardown itself blocks (seen once with
+        # captured collectives); the result line is already out.
+        import threading
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        sg = wg = sgs = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 def sweep_rows(torch, Q, harness, fused, fp16, device, l2, peak, seed):

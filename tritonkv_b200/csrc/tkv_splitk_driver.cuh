@@ -580,11 +580,20 @@ struct SplitLaunch {
                     cudaStream_t stream) {
     int rc = prepare();
     if (rc != TKV_OK) return rc;
-    // Programmatic dependent launch: the prologue (barrier set-up, schedule arithmetic)
-    // overlaps the tail of the previous kernel of the stream; the kernel itself waits for
-    // that kernel's completion before its first global access.
-    TKV_CUDA(launch_pdl(splitk_kernel<Policy>, dim3(sc.grid), dim3(Policy::WARPS * 32),
-                        (size_t)smem_bytes(), stream, maps, p, sc));
+    // Unit-aligned plans (small batches, CTAs of a few microseconds) are launched as
+    // programmatic dependents: the prologue overlaps the tail of the previous kernel of the
+    // stream and the kernel waits for that kernel's completion before its first global
+    // access.  The balanced global plan is launched plainly: its CTAs run for tens of
+    // microseconds and all of them must be resident together, and measured under graph
+    // replay a dependent launch placed one CTA per still-resident combine CTA late (by
+    // 10-30 us at batch 16-32), which the static tile ranges cannot absorb.
+    if (sc.persistent == 2) {
+      TKV_CUDA(launch_pdl(splitk_kernel<Policy>, dim3(sc.grid), dim3(Policy::WARPS * 32),
+                          (size_t)smem_bytes(), stream, maps, p, sc));
+    } else {
+      splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem_bytes(), stream>>>(maps, p, sc);
+      TKV_CUDA(cudaGetLastError());
+    }
     return TKV_OK;
   }
   static int attrs(int* regs, int* smem, int* local, int* ctas) {
