@@ -289,7 +289,8 @@ def run_ours(args):
         def make_step(i):
             r = reps[i]
             return lambda: dec.step(r["q"], r["kq"], r["vq"])
-        launches_per_step = 3  # split, local merge, cross-rank merge (+ one NCCL all-gather)
+        # split, local merge, cross-rank merge (+ one NCCL all-gather unless peer stores are used)
+        launches_per_step = 3
     else:
         def make_step(i):
             r = reps[i]
@@ -421,7 +422,9 @@ def run_ours(args):
                 "regime": f"cold: inputs larger than L2 ({R} distinct caches, "
                           f"{R * cbytes / 1e6:.0f} MB >= 3 x {l2 / 1e6:.0f} MB L2), "
                           + ("CUDA-graph replay" if graphs else "direct launches"),
-                "partition": ("history split over ranks + NCCL all-gather of (acc,m,l) + combine"
+                "partition": ((f"history split over ranks; exchange of (acc,m,l): "
+                               + ("stores into peer memory + flags" if dec.exchange == "peer"
+                                  else "one NCCL all-gather") + "; log-sum-exp merge")
                               if history_split else "independent sequences per rank, no collective"),
                 "partial_slots_per_head": (ws.get("key") or (0, 0, 1, 0))[2],
                 "untimed_steps_before_timing": K + W if graphs else 3 * R + W,

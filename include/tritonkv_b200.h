@@ -158,10 +158,43 @@ int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t* k_packed,
                             const void* v_scale, const void* v_zero, float* out, int B, int HQ,
                             int HKV, int S, int D, int nbits, int gs, float sm_scale, void* stream);
 
+/* Quantise T_new new tokens per (sequence, head) -- x (B, HKV, T_new, D) -- and write them
+ * into a preallocated cache of S_cap token rows per (sequence, head): packed
+ * (B, HKV, S_cap, D*nbits/8), scale / zero (B, HKV, S_cap, D/gs), at rows positions[b] + t
+ * (positions int32 (B,) on the device, or null for pos0 everywhere).  Same arithmetic as
+ * tkv_quantize_pack, so a cache filled token by token is byte-identical to quantising the
+ * whole tensor at once.  Tokens that would fall outside [0, S_cap) are dropped.  No
+ * reference counterpart: quantize.py:186-236 quantises whole tensors; this is the write
+ * side of a decode loop that grows the cache one token per step. */
+int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed, void* scale, void* zero, int B,
+                        int HKV, int T_new, int64_t S_cap, int D, int nbits, int gs,
+                        const int32_t* positions, int pos0, void* stream);
+
+/* Cross-GPU exchange for a history split over the GPUs of one node (no reference
+ * counterpart: the reference is single-GPU).  Each rank owns a receive buffer of
+ * 2 * world blocks of `wire_floats` 8-byte pairs {value, step} in the layout
+ * [acc rows*D | m rows | l rows], and two 32-bit state words {step, tickets} in its own
+ * memory, all zeroed before the first call; the receive buffers are mapped on every rank
+ * (peer or symmetric memory) and passed as a table of `world` pointers, entry j = rank j's.
+ * tkv_combine_push merges this rank's split partials (arguments as tkv_combine_strided,
+ * result left unnormalised) and stores them, tagged with the step number, into block
+ * (step parity, rank) of every rank's buffer.  tkv_merge_wait, enqueued after it on the
+ * same stream, reads the world blocks of this step -- polling each pair until it carries
+ * the step -- merges them into out (rows, D) and bumps the step.  The wait is bounded
+ * (about 0.2 s); on expiry the kernel records bit 1 of tkv_device_status and merges what
+ * it has.  Ranks must call the pair in lockstep, one pair per decode step. */
+int tkv_combine_push(const float* acc, const float* m, const float* l, int64_t rows, int NS, int D,
+                     int64_t acc_row_stride, int64_t acc_slot_stride, int64_t ml_row_stride,
+                     int64_t ml_slot_stride, void* const* peer_data, void* state, int world,
+                     int rank, int wire_floats, void* stream);
+int tkv_merge_wait(float* out, int64_t rows, int D, void* const* peer_data, void* state, int world,
+                   int rank, int wire_floats, void* stream);
+
 /* Device-side status word of the current device (synchronises with it): 0 = ok,
- * 1 = a bounded wait on a copy barrier inside a decode kernel gave up (the kernel then
- * returned early and its output is invalid).  No reference counterpart: the Triton
- * kernels have no waits of their own. */
+ * bit 0 = a bounded wait on a copy barrier inside a decode kernel gave up (the kernel then
+ * returned early and its output is invalid), bit 1 = a bounded wait for a peer's data in
+ * tkv_merge_wait gave up.  No reference counterpart: the Triton kernels have no waits of
+ * their own. */
 int tkv_device_status(int* status);
 
 #ifdef __cplusplus

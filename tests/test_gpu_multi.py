@@ -41,15 +41,20 @@ def _worker(rank, world, port, ret):
         cut = lambda t: Q.QuantizedTensor(t.packed[:, :, lo:hi].contiguous(),
                                           t.scale[:, :, lo:hi].contiguous(),
                                           t.zero[:, :, lo:hi].contiguous(), 2, 32, D)
-        dec = P.HistorySplitDecoder(B, HQ, D, dev)
-        out = dec.step(q, cut(kq), cut(vq)).clone()
-        out2 = dec.step(q, cut(kq), cut(vq))  # buffers are reused across steps
-        torch.cuda.synchronize()
         to_o = lambda t: O.OracleQuantized(t.packed.cpu().numpy(), t.scale.cpu().numpy(),
                                            t.zero.cpu().numpy(), 2, 32, D)
         ref = O.reference_on_quantized(q.float().cpu().numpy(), to_o(kq), to_o(vq))
-        rep = O.allclose_report(out.cpu().numpy(), ref)
-        ok_hist = rep["ok"] and rep["cosine"] >= 0.99999 and torch.equal(out, out2)
+        ok_hist, exchanges = True, []
+        for exchange in ("nccl", "auto"):  # auto: stores into peer memory where it can be set up
+            dec = P.HistorySplitDecoder(B, HQ, D, dev, exchange=exchange)
+            exchanges.append(dec.exchange)
+            outs = [dec.step(q, cut(kq), cut(vq)).clone() for _ in range(5)]  # buffers are reused
+            torch.cuda.synchronize()
+            rep = O.allclose_report(outs[0].cpu().numpy(), ref)
+            ok_hist = (ok_hist and rep["ok"] and rep["cosine"] >= 0.99999
+                       and all(torch.equal(outs[0], o) for o in outs[1:]))
+        from tritonkv_b200 import _cabi
+        ok_hist = ok_hist and _cabi.device_status() == 0
         # ---- batch sharding: nothing is exchanged, every rank checks its own shard ----
         B2 = 6
         q2, k2, v2 = make_random_kv(B2, 32, 8, 700, D, device=dev, seed=124)
@@ -64,7 +69,7 @@ def _worker(rank, world, port, ret):
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
         if rank == 0:
             ret["hist"], ret["batch"] = bool(flags[0].item()), bool(flags[1].item())
-            ret["rep"] = str(rep)
+            ret["rep"] = str(rep) + " exchanges=" + str(exchanges)
     finally:
         dist.destroy_process_group()
 

@@ -146,3 +146,66 @@ def test_quantize_kv_full_size_round_trip_property():
     deq = Q.dequantize_groupwise(qt, torch.float32)
     step = qt.scale.float().repeat_interleave(32, dim=-1)
     assert torch.all((deq - k.float()).abs() <= step / 2 + 1e-2 * step + 1e-6)
+
+
+# ---- appending tokens to a preallocated cache (no reference counterpart: the property
+# ---- is that a cache filled step by step equals quantising the whole tensor at once)
+@pytest.mark.parametrize("nbits", Q.SUPPORTED_BITS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_append_equals_whole_tensor_quantisation(nbits, dtype):
+    torch.manual_seed(5)
+    B, HKV, S, D, gs = 3, 2, 37, 128, 32
+    x = (torch.randn(B, HKV, S, D, device=DEV) * 1.7).to(dtype)
+    whole = Q.quantize_groupwise(x, nbits, gs)
+    cache = Q.empty_cache(B, HKV, S + 5, D, nbits, gs, DEV)
+    # a prefill chunk, then single tokens, then a ragged tail through per-sequence positions
+    Q.append_groupwise(cache, x[:, :, :16], 0)
+    for t in range(16, 30):
+        Q.append_groupwise(cache, x[:, :, t:t + 1], t)
+    pos = torch.full((B,), 30, dtype=torch.int32, device=DEV)
+    Q.append_groupwise(cache, x[:, :, 30:], pos)
+    assert torch.equal(cache.packed[:, :, :S], whole.packed)
+    assert torch.equal(cache.scale[:, :, :S].view(torch.int16), whole.scale.view(torch.int16))
+    assert torch.equal(cache.zero[:, :, :S].view(torch.int16), whole.zero.view(torch.int16))
+    assert int(cache.packed[:, :, S:].max()) == 0 and float(cache.scale[:, :, S:].abs().max()) == 0.0
+
+
+def test_append_per_sequence_positions_and_decode():
+    """Sequences of different lengths grow in one cache; decoding it with seq_lens equals
+    decoding each sequence's own dense cache."""
+    from tritonkv_b200.kernels import fused_decode_attention
+
+    torch.manual_seed(6)
+    B, HQ, HKV, D, gs, nbits, cap = 3, 8, 2, 128, 32, 4, 96
+    lens = [17, 64, 41]
+    k = torch.randn(B, HKV, cap, D, device=DEV, dtype=torch.float16)
+    v = torch.randn(B, HKV, cap, D, device=DEV, dtype=torch.float16)
+    q = torch.randn(B, HQ, D, device=DEV, dtype=torch.float16)
+    kq = Q.empty_cache(B, HKV, cap, D, nbits, gs, DEV)
+    vq = Q.empty_cache(B, HKV, cap, D, nbits, gs, DEV)
+    pos = torch.zeros(B, dtype=torch.int32, device=DEV)
+    for t in range(max(lens)):
+        # every sequence appends its token t; finished sequences send theirs out of range
+        p = torch.tensor([t if t < n else cap for n in lens], dtype=torch.int32, device=DEV)
+        Q.append_kv(kq, vq, k[:, :, t:t + 1], v[:, :, t:t + 1], p)
+    seq = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = fused_decode_attention(q, kq, vq, seq_lens=seq)
+    for b, n in enumerate(lens):
+        kb, vb = Q.quantize_kv(k[b:b + 1, :, :n].contiguous(), v[b:b + 1, :, :n].contiguous(), nbits, gs)
+        assert torch.equal(kq.packed[b, :, :n], kb.packed[0])
+        ref = fused_decode_attention(q[b:b + 1], kb, vb)
+        assert torch.allclose(got[b], ref[0], atol=2e-5, rtol=1e-4)
+        assert int(kq.packed[b, :, n:].max()) == 0  # dropped tokens wrote nothing
+
+
+def test_append_argument_errors():
+    cache = Q.empty_cache(2, 2, 8, 128, 4, 32, DEV)
+    x = torch.randn(2, 2, 4, 128, device=DEV, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        Q.append_groupwise(cache, x, 6)  # 6 + 4 > 8
+    with pytest.raises(ValueError):
+        Q.append_groupwise(cache, x[:, :1], 0)  # head mismatch
+    with pytest.raises(ValueError):
+        Q.append_groupwise(cache, x, torch.zeros(2, dtype=torch.int64, device=DEV))
+    with pytest.raises(RuntimeError):
+        Q.append_groupwise(cache, x.cpu(), 0)

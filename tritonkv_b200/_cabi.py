@@ -57,6 +57,13 @@ SIGNATURES = {
     "tkv_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, POINTER(c_int), POINTER(c_int)]),
     "tkv_device_status": (c_int, [POINTER(c_int)]),
+    "tkv_quantize_append": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                    c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "tkv_combine_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int64,
+                                 c_int64, c_int64, POINTER(c_void_p), c_void_p, c_int, c_int, c_int,
+                                 c_void_p]),
+    "tkv_merge_wait": (c_int, [c_void_p, c_int64, c_int, POINTER(c_void_p), c_void_p, c_int, c_int,
+                               c_int, c_void_p]),
     "tkv_fused_decode_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_float, c_void_p]),

@@ -18,6 +18,7 @@ int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int*
 int fp16_attrs(int D, int* regs, int* smem, int* local, int* ctas);
 int fused_device_status(int* status);
 int fp16_device_status(int* status);
+int exchange_device_status(int* status);
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
                int num_splits, int split_size, bool ragged);
 int fp16_plan(int D, SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
@@ -104,11 +105,13 @@ extern "C" int tkv_wave_programs(int kernel_id, int nbits, int D, int gs, int* p
 
 extern "C" int tkv_device_status(int* status) {
   TKV_REQUIRE(status, TKV_ERR_INVALID, "device_status: null output");
-  int a = 0, b = 0;
+  int a = 0, b = 0, c = 0;
   int rc = fused_device_status(&a);
   if (rc != TKV_OK) return rc;
   rc = fp16_device_status(&b);
   if (rc != TKV_OK) return rc;
-  *status = a | b;
+  rc = exchange_device_status(&c);
+  if (rc != TKV_OK) return rc;
+  *status = a | b | (c << 1);
   return TKV_OK;
 }

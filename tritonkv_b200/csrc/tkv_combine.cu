@@ -17,26 +17,32 @@ namespace tkv {
 constexpr int kCombineThreads = 256;
 constexpr int kCombineSlice = 32;  // head dims per CTA
 
-__global__ void __launch_bounds__(kCombineThreads)
-    combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
-                   const float* __restrict__ l, float* __restrict__ out, float* __restrict__ out_m,
-                   float* __restrict__ out_l, int NS, int D, int64_t a_row, int64_t a_slot,
-                   int64_t ml_row, int64_t ml_slot) {
+// What thread `tid` < 8 of a CTA holds after the block-wide merge of one (row, 32-dim slice).
+struct CombineResult {
+  float4 r;  // unnormalised sum_s acc_s 2^(m_s - M), dims d0 + 4 tid .. +3
+  float M;   // max_s m_s
+  float L;   // sum_s l_s 2^(m_s - M)
+};
+
+__device__ __forceinline__ CombineResult combine_reduce(const float* __restrict__ acc,
+                                                        const float* __restrict__ m,
+                                                        const float* __restrict__ l, int NS,
+                                                        int64_t a_row, int64_t a_slot,
+                                                        int64_t ml_row, int64_t ml_slot, int row,
+                                                        int d0) {
+  CombineResult res;
+  res.r = make_float4(0.f, 0.f, 0.f, 0.f);
+  res.L = 0.f;
   __shared__ float red_m[8];
   __shared__ float4 red_a[8][8];
   __shared__ float red_l[8];
   __shared__ float sh_m[kCombineThreads];
   __shared__ float sh_l[kCombineThreads];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row = blockIdx.x;            // b*HQ + h
-  const int d0 = blockIdx.y * kCombineSlice;
   const int sg = tid >> 3, dl = tid & 7; // split group (0..31), float4 index inside the slice
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
   const float* arow = acc + (int64_t)row * a_row + d0 + dl * 4;
-
-  pdl_launch_dependents();  // the next kernel of the stream may start its prologue
-  pdl_wait();  // partials come from the kernel launched just before this one
 
   constexpr int kCached = 8;  // slots per thread kept in registers: NS <= 256
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -128,18 +134,171 @@ __global__ void __launch_bounds__(kCombineThreads)
       r.w += x.w;
       Lt += red_l[w];
     }
+    res.r = r;
+    res.L = Lt;
+  }
+  res.M = M;
+  return res;
+}
+
+__global__ void __launch_bounds__(kCombineThreads)
+    combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                   const float* __restrict__ l, float* __restrict__ out, float* __restrict__ out_m,
+                   float* __restrict__ out_l, int NS, int D, int64_t a_row, int64_t a_slot,
+                   int64_t ml_row, int64_t ml_slot) {
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;  // b*HQ + h
+  const int d0 = blockIdx.y * kCombineSlice;
+  pdl_launch_dependents();  // the next kernel of the stream may start its prologue
+  pdl_wait();               // partials come from the kernel launched just before this one
+  const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
+  if (tid < 8) {
+    float4 r = c.r;
     if (out_m == nullptr) {
-      const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
+      const float inv = c.L > 0.f ? 1.f / c.L : 0.f;
       r.x *= inv;
       r.y *= inv;
       r.z *= inv;
       r.w *= inv;
     } else if (tid == 0 && blockIdx.y == 0) {
-      out_m[row] = M;
-      out_l[row] = Lt;
+      out_m[row] = c.M;
+      out_l[row] = c.L;
     }
     *reinterpret_cast<float4*>(out + (int64_t)row * D + d0 + tid * 4) = r;
   }
+}
+
+// ---------------------------------------------------------------------------------
+// Cross-GPU exchange of one merged partial per head over peer memory (history split).
+//
+// Every rank owns a receive buffer of 2 x world blocks, mapped on every peer.  A block is
+// the wire layout [acc rows*D | m rows | l rows] with every float widened to the 8-byte
+// pair {value, step}: an 8-byte store is delivered whole, so the step number that rides
+// with each value tells the reader that THIS value has arrived -- no fence, no flag, no
+// acknowledgement on the path, one NVLink latency (a fenced data-then-flag version of
+// this exchange cost three).  push merges the local split partials like combine_kernel
+// and stores the result into block (step parity, own rank) of EVERY rank's buffer.
+// wait-merge reads the world blocks of this step, each thread polling its own pairs until
+// they carry the step (bounded; on expiry it records a status and goes on), merges them,
+// and the last CTA to finish (a ticket counter on local memory) bumps the step.  Two
+// parities suffice: a rank can only be one step ahead of the slowest, because each step
+// consumes every rank's block.
+constexpr int kMaxPeers = 8;
+struct Exchange {
+  uint2* data[kMaxPeers];  // rank j's receive buffer, as mapped in this process
+  uint32_t* state;         // this rank's {step, tickets}, local memory
+  int world, rank, rows, wire;  // wire = pairs per block
+};
+
+__device__ int g_exchange_status;  // 0 ok, 1 a bounded wait for a peer's data gave up
+
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_volatile_pair(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_pair(uint2* p, float x, uint32_t step) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};\n" ::"l"(p), "r"(__float_as_uint(x)), "r"(step)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kCombineThreads)
+    combine_push_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                        const float* __restrict__ l, int NS, int D, int64_t a_row, int64_t a_slot,
+                        int64_t ml_row, int64_t ml_slot, const Exchange ex) {
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;
+  const int d0 = blockIdx.y * kCombineSlice;
+  pdl_launch_dependents();
+  pdl_wait();
+  const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
+  if (tid < 8) {
+    const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the wait-merge kernel only
+    const int64_t blk = (int64_t)((step & 1) * ex.world + ex.rank) * ex.wire;
+    const int64_t e = (int64_t)row * D + d0 + tid * 4;
+    for (int j = 0; j < ex.world; ++j) {
+      uint2* dst = ex.data[j] + blk;
+      st_volatile_pair(dst + e, c.r.x, step);
+      st_volatile_pair(dst + e + 1, c.r.y, step);
+      st_volatile_pair(dst + e + 2, c.r.z, step);
+      st_volatile_pair(dst + e + 3, c.r.w, step);
+      if (tid == 0 && blockIdx.y == 0) {
+        st_volatile_pair(dst + (int64_t)ex.rows * D + row, c.M, step);
+        st_volatile_pair(dst + (int64_t)ex.rows * D + ex.rows + row, c.L, step);
+      }
+    }
+  }
+}
+
+// One CTA per (row, 32-dim slice): warp j reads rank j's block, lane = dim inside the slice.
+__global__ void __launch_bounds__(kCombineThreads)
+    merge_wait_kernel(float* __restrict__ out, int D, const Exchange ex) {
+  __shared__ float sh_x[kMaxPeers][kCombineSlice];
+  __shared__ float sh_ml[kMaxPeers][2];
+  const int tid = threadIdx.x, j = tid >> 5, lane = tid & 31;
+  const int row = blockIdx.x;
+  const int d0 = blockIdx.y * kCombineSlice;
+  pdl_launch_dependents();
+  pdl_wait();  // orders this kernel after the previous wait-merge (the step counter) and the push
+  const uint32_t step = ld_volatile_u32(ex.state) + 1;
+  if (j < ex.world) {
+    const uint2* src = ex.data[ex.rank] + (int64_t)((step & 1) * ex.world + j) * ex.wire;
+    const uint2* px = src + (int64_t)row * D + d0 + lane;
+    // lanes 0 and 1 also fetch (m, l) of the row
+    const uint2* pml = src + (int64_t)ex.rows * D + (lane == 1 ? ex.rows : 0) + row;
+    uint2 x = ld_volatile_pair(px);
+    uint2 ml = lane < 2 ? ld_volatile_pair(pml) : make_uint2(0u, step);
+    int polls = 0;
+    while (x.y != step || ml.y != step) {
+      if (++polls > (1 << 21)) {  // ~0.2 s with the pause below: a peer is gone
+        atomicExch(&g_exchange_status, 1);
+        break;
+      }
+      __nanosleep(100);
+      if (x.y != step) x = ld_volatile_pair(px);
+      if (ml.y != step) ml = ld_volatile_pair(pml);
+    }
+    sh_x[j][lane] = __uint_as_float(x.x);
+    if (lane < 2) sh_ml[j][lane] = __uint_as_float(ml.x);
+  }
+  __syncthreads();
+  if (tid < kCombineSlice) {
+    float M = -INFINITY;
+    for (int r = 0; r < ex.world; ++r) M = fmaxf(M, sh_ml[r][0]);
+    float a = 0.f, L = 0.f;
+    for (int r = 0; r < ex.world; ++r) {
+      const float mr = sh_ml[r][0];
+      if (mr > -INFINITY) {  // a rank without tokens sends m = -inf
+        const float w = ex2(mr - M);
+        a = fmaf(w, sh_x[r][tid], a);
+        L = fmaf(w, sh_ml[r][1], L);
+      }
+    }
+    out[(int64_t)row * D + d0 + tid] = L > 0.f ? a / L : 0.f;
+  }
+  // the last CTA to get here bumps the step (local memory only; nothing waits on it
+  // inside this grid, and the next push follows this grid in the stream)
+  if (tid == 0) {
+    const uint32_t total = gridDim.x * gridDim.y;
+    const uint32_t ticket = atomicAdd(ex.state + 1, 1u);
+    if (ticket == total - 1) {
+      ex.state[1] = 0;
+      __threadfence();
+      ex.state[0] = step;
+    }
+  }
+}
+
+int exchange_device_status(int* status) {
+  int v = 0;
+  TKV_CUDA(cudaMemcpyFromSymbol(&v, g_exchange_status, sizeof(int)));
+  *status = v;
+  return TKV_OK;
 }
 
 // Few partials per row (large batches: 2-8 slots): one warp per (batch, head), each
@@ -259,4 +418,64 @@ extern "C" int tkv_combine(const float* acc, const float* m, const float* l, flo
               "combine: bad sizes B=%d HQ=%d NS=%d D=%d", B, HQ, NS, D);
   return tkv_combine_strided(acc, m, l, out, out_m, out_l, (int64_t)B * HQ, NS, D,
                              (int64_t)NS * D, D, NS, 1, stream);
+}
+
+namespace {
+int fill_exchange(tkv::Exchange& ex, void* const* peer_data, void* state, int world, int rank,
+                  int64_t rows, int D, int wire_floats) {
+  using namespace tkv;
+  TKV_REQUIRE(peer_data && state, TKV_ERR_INVALID, "exchange: null pointer table");
+  TKV_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, TKV_ERR_INVALID,
+              "exchange: bad rank %d of %d (at most %d ranks)", rank, world, kMaxPeers);
+  TKV_REQUIRE(rows > 0 && rows <= 0x7fffffffLL && D > 0 && D % kCombineSlice == 0, TKV_ERR_INVALID,
+              "exchange: bad sizes rows=%lld D=%d", (long long)rows, D);
+  TKV_REQUIRE((int64_t)wire_floats >= rows * (D + 2), TKV_ERR_INVALID,
+              "exchange: a block of %d values cannot hold %lld rows of D=%d plus (m, l)", wire_floats,
+              (long long)rows, D);
+  for (int j = 0; j < world; ++j) {
+    TKV_REQUIRE(peer_data[j], TKV_ERR_INVALID, "exchange: null buffer of rank %d", j);
+    TKV_REQUIRE((reinterpret_cast<uintptr_t>(peer_data[j]) & 7u) == 0, TKV_ERR_ALIGN,
+                "exchange: buffer of rank %d not 8-byte aligned", j);
+    ex.data[j] = static_cast<uint2*>(peer_data[j]);
+  }
+  ex.state = static_cast<uint32_t*>(state);
+  ex.world = world;
+  ex.rank = rank;
+  ex.rows = (int)rows;
+  ex.wire = wire_floats;
+  return TKV_OK;
+}
+}  // namespace
+
+extern "C" int tkv_combine_push(const float* acc, const float* m, const float* l, int64_t rows, int NS,
+                                int D, int64_t acc_row_stride, int64_t acc_slot_stride,
+                                int64_t ml_row_stride, int64_t ml_slot_stride,
+                                void* const* peer_data, void* state, int world, int rank,
+                                int wire_floats, void* stream) {
+  using namespace tkv;
+  TKV_REQUIRE(acc && m && l, TKV_ERR_INVALID, "combine_push: null pointer");
+  TKV_REQUIRE(NS > 0, TKV_ERR_INVALID, "combine_push: NS=%d", NS);
+  TKV_REQUIRE(aligned16(acc) && acc_row_stride % 4 == 0 && acc_slot_stride % 4 == 0, TKV_ERR_ALIGN,
+              "combine_push: acc must be 16-byte aligned, strides multiples of 4");
+  Exchange ex{};
+  int rc = fill_exchange(ex, peer_data, state, world, rank, rows, D, wire_floats);
+  if (rc != TKV_OK) return rc;
+  dim3 grid((unsigned)rows, D / kCombineSlice);
+  TKV_CUDA(launch_pdl(tkv::combine_push_kernel, grid, dim3(kCombineThreads), 0, (cudaStream_t)stream,
+                      acc, m, l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
+                      ml_slot_stride, ex));
+  return TKV_OK;
+}
+
+extern "C" int tkv_merge_wait(float* out, int64_t rows, int D, void* const* peer_data, void* state,
+                              int world, int rank, int wire_floats, void* stream) {
+  using namespace tkv;
+  TKV_REQUIRE(out, TKV_ERR_INVALID, "merge_wait: null out");
+  Exchange ex{};
+  int rc = fill_exchange(ex, peer_data, state, world, rank, rows, D, wire_floats);
+  if (rc != TKV_OK) return rc;
+  dim3 grid((unsigned)rows, D / kCombineSlice);
+  TKV_CUDA(launch_pdl(tkv::merge_wait_kernel, grid, dim3(kCombineThreads), 0, (cudaStream_t)stream, out,
+                      D, ex));
+  return TKV_OK;
 }

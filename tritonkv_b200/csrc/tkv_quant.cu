@@ -48,11 +48,20 @@ __device__ __forceinline__ void load8<float>(const float* p, float (&x)[8]) {
   x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
 
+// Where the rows go when new tokens are appended to a preallocated cache (cap == 0: in place).
+struct AppendMap {
+  const int32_t* pos;  // per-sequence first free slot, or null for pos0 everywhere
+  int pos0;
+  int t_new;           // new tokens per (sequence, head)
+  int hkv;             // heads per sequence
+  int64_t cap;         // token rows per (sequence, head) in the cache
+};
+
 template <typename T, int NBITS>
 __global__ void __launch_bounds__(256)
     quantize_pack_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed,
                          __half* __restrict__ scale, __half* __restrict__ zero, int64_t rows,
-                         int D, int gs) {
+                         int D, int gs, const AppendMap am) {
   constexpr int P = 8 / NBITS;
   constexpr float QMAX = float((1 << NBITS) - 1);
   const int tpr = D >> 3;                 // threads per row
@@ -98,10 +107,21 @@ __global__ void __launch_bounds__(256)
     const uint32_t hi = __shfl_xor_sync(kFullMask, (uint32_t)(word >> 32), off);
     word |= ((uint64_t)hi << 32) | lo;
   }
-  if (live) {
-    if (p == 0) *reinterpret_cast<uint64_t*>(packed + row * (D / P) + 8 * c) = word;
+  // Output row: the input row itself, or (append) slot pos[b] + t of sequence (b, head)
+  // in a cache of `cap` token rows per sequence; tokens that fall outside are dropped.
+  int64_t orow = row;
+  bool keep = live;
+  if (am.cap > 0 && live) {
+    const int64_t bh = row / am.t_new;
+    const int t = (int)(row - bh * am.t_new);
+    const int64_t at = (am.pos ? (int64_t)am.pos[bh / am.hkv] : (int64_t)am.pos0) + t;
+    keep = at >= 0 && at < am.cap;
+    orow = bh * am.cap + at;
+  }
+  if (keep) {
+    if (p == 0) *reinterpret_cast<uint64_t*>(packed + orow * (D / P) + 8 * c) = word;
     if ((c % lanes_per_group) == 0) {
-      const int64_t gi = row * (D / gs) + (8 * c) / gs;
+      const int64_t gi = orow * (D / gs) + (8 * c) / gs;
       scale[gi] = sc16;
       zero[gi] = ze16;
     }
@@ -211,16 +231,16 @@ extern "C" int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t r
 namespace {
 template <typename T>
 int launch_quantize(const void* x, uint8_t* packed, void* scale, void* zero, int64_t rows, int D,
-                    int nbits, int gs, cudaStream_t stream) {
+                    int nbits, int gs, cudaStream_t stream, const AppendMap am = AppendMap{}) {
   const int64_t threads = rows * (D / 8);
   const int64_t blocks = (threads + 255) / 256;
   TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "quantize_pack: tensor too large");
   if (nbits == 4)
     quantize_pack_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs);
+        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs, am);
   else
     quantize_pack_kernel<T, 2><<<(int)blocks, 256, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs);
+        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs, am);
   TKV_CUDA(cudaGetLastError());
   return TKV_OK;
 }
@@ -250,6 +270,46 @@ extern "C" int tkv_quantize_pack(const void* x, int in_dtype, uint8_t* packed, v
     case TKV_DTYPE_F32: return launch_quantize<float>(x, packed, scale, zero, rows, D, nbits, gs, s);
   }
   set_error("quantize_pack: bad dtype %d", in_dtype);
+  return TKV_ERR_INVALID;
+}
+
+static int check_quantize_shape(const char* who, int D, int nbits, int gs) {
+  TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
+  TKV_REQUIRE(gs > 0 && D > 0 && D % gs == 0, TKV_ERR_INVALID,
+              "group_size %d must divide head_dim %d", gs, D);
+  TKV_REQUIRE(pow2(D) && D >= 16 && D <= 256 && pow2(gs) && gs >= 8, TKV_ERR_UNSUPPORTED,
+              "%s: built for power-of-two head_dim in [16, 256] and power-of-two "
+              "group_size >= 8 (got head_dim=%d, group_size=%d)", who, D, gs);
+  TKV_REQUIRE((D * nbits / 8) % 8 == 0, TKV_ERR_UNSUPPORTED,
+              "%s: packed row of %d bytes is not a multiple of 8", who, D * nbits / 8);
+  return TKV_OK;
+}
+
+extern "C" int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed, void* scale,
+                                   void* zero, int B, int HKV, int T_new, int64_t S_cap, int D,
+                                   int nbits, int gs, const int32_t* positions, int pos0,
+                                   void* stream) {
+  TKV_REQUIRE(x && packed && scale && zero, TKV_ERR_INVALID, "quantize_append: null pointer");
+  TKV_REQUIRE(B > 0 && HKV > 0 && T_new >= 0 && S_cap > 0, TKV_ERR_INVALID,
+              "quantize_append: bad sizes B=%d HKV=%d T_new=%d S_cap=%lld", B, HKV, T_new,
+              (long long)S_cap);
+  int rc = check_quantize_shape("quantize_append", D, nbits, gs);
+  if (rc != TKV_OK) return rc;
+  TKV_REQUIRE(aligned16(x) && ((uintptr_t)packed & 7u) == 0, TKV_ERR_ALIGN,
+              "quantize_append: x must be 16-byte and packed 8-byte aligned");
+  TKV_REQUIRE(positions != nullptr || (pos0 >= 0 && (int64_t)pos0 + T_new <= S_cap), TKV_ERR_INVALID,
+              "quantize_append: tokens [%d, %d) do not fit a cache of %lld rows", pos0, pos0 + T_new,
+              (long long)S_cap);
+  if (T_new == 0) return TKV_OK;
+  AppendMap am{positions, pos0, T_new, HKV, S_cap};
+  const int64_t rows = (int64_t)B * HKV * T_new;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (in_dtype) {
+    case TKV_DTYPE_F16: return launch_quantize<__half>(x, packed, scale, zero, rows, D, nbits, gs, s, am);
+    case TKV_DTYPE_BF16: return launch_quantize<__nv_bfloat16>(x, packed, scale, zero, rows, D, nbits, gs, s, am);
+    case TKV_DTYPE_F32: return launch_quantize<float>(x, packed, scale, zero, rows, D, nbits, gs, s, am);
+  }
+  set_error("quantize_append: bad dtype %d", in_dtype);
   return TKV_ERR_INVALID;
 }
 

@@ -12,11 +12,20 @@ only thing that ever crosses a link.
   ``B*HQ*(D+2)`` floats in a single collective, and every rank finishes with the same
   log-sum-exp merge kernel that combines intra-GPU splits (``NS = world``).
 
+  The exchange has two forms: one NCCL all-gather (``exchange="nccl"``), or stores into
+  every peer's receive buffer through symmetric memory with a flag per rank
+  (``exchange="peer"``, :class:`PeerExchange`): the local merge kernel writes its result
+  straight into the peers' buffers as {value, step} pairs and the cross-rank merge kernel
+  waits, bounded, until the pairs of this step have arrived -- no collective launch, no
+  fence, one NVLink latency.
+
 The plan functions are pure Python and backend-agnostic so the multi-rank logic is
 testable with the ``gloo`` backend on CPU tensors; only the compute calls need CUDA.
 """
 
 from __future__ import annotations
+
+import ctypes
 
 import torch
 
@@ -98,14 +107,77 @@ def merge_gathered(gathered: torch.Tensor, B: int, HQ: int, D: int,
     return out
 
 
-class HistorySplitDecoder:
-    """Single-sequence long-context decode with the history split over the ranks of
-    ``group``.  Buffers are allocated once; ``step`` enqueues: local split kernel ->
-    local merge into the wire buffer -> one all-gather -> cross-rank merge."""
+def exchange_layout(world: int, wire: int) -> tuple[int, int]:
+    """Byte offset of the state words and total bytes of one rank's symmetric buffer:
+    ``2 * world`` blocks of ``wire`` 8-byte pairs {value, step} | {step, tickets}."""
+    state_off = 2 * world * wire * 8
+    return state_off, state_off + 16
+
+
+class PeerExchange:
+    """Receive buffers of all ranks mapped on every rank (torch symmetric memory) and the
+    two kernels that use them: ``push`` (local merge stored into every rank's buffer as
+    {value, step} pairs) and ``wait_merge`` (bounded wait until every pair of this step has
+    arrived, then the cross-rank merge).  Ranks call the pair in lockstep, once per decode step."""
 
     def __init__(self, B: int, HQ: int, D: int, device, group=None):
         import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
 
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the peer exchange serves at most 8 ranks")
+        self.rows, self.D, self.wire = B * HQ, D, wire_floats(B, HQ, D)
+        state_off, total = exchange_layout(self.world, self.wire)
+        self.buf = symm_mem.empty(total // 4, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        dist.barrier(group)  # every rank has zeroed its buffer before anyone pushes
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        table = ctypes.c_void_p * self.world
+        self.data_ptrs = table(*ptrs)
+        self.state_ptr = ptrs[self.rank] + state_off
+
+    def push(self, acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor) -> None:
+        """``acc (B, HQ, NS, D)``, ``m, l (B, HQ, NS)``: this rank's split partials."""
+        NS = acc.shape[2]
+        with torch.cuda.device(acc.device):
+            _cabi.check(_cabi.load().tkv_combine_push(
+                acc.data_ptr(), m.data_ptr(), l.data_ptr(), self.rows, NS, self.D, NS * self.D, self.D,
+                NS, 1, self.data_ptrs, self.state_ptr, self.world, self.rank, self.wire,
+                _cabi.stream_ptr(acc.device)))
+
+    def push_empty(self, scratch: dict, device) -> None:
+        """A rank without tokens contributes the neutral partial (m = -inf, l = 0)."""
+        if "acc" not in scratch:
+            scratch["acc"] = torch.zeros(self.rows, 1, self.D, device=device, dtype=torch.float32)
+            scratch["m"] = torch.full((self.rows, 1), float("-inf"), device=device, dtype=torch.float32)
+            scratch["l"] = torch.zeros(self.rows, 1, device=device, dtype=torch.float32)
+        a = scratch["acc"]
+        self.push(a.view(1, self.rows, 1, self.D) if a.dim() == 3 else a, scratch["m"], scratch["l"])
+
+    def wait_merge(self, out: torch.Tensor) -> torch.Tensor:
+        with torch.cuda.device(out.device):
+            _cabi.check(_cabi.load().tkv_merge_wait(
+                out.data_ptr(), self.rows, self.D, self.data_ptrs, self.state_ptr, self.world,
+                self.rank, self.wire, _cabi.stream_ptr(out.device)))
+        return out
+
+
+class HistorySplitDecoder:
+    """Single-sequence long-context decode with the history split over the ranks of
+    ``group``.  Buffers are allocated once; ``step`` enqueues: local split kernel ->
+    local merge -> exchange -> cross-rank merge.  ``exchange``: ``"nccl"`` (one
+    all-gather), ``"peer"`` (stores into peer memory, see :class:`PeerExchange`) or
+    ``"auto"`` (peer when symmetric memory can be set up on every rank, else NCCL)."""
+
+    def __init__(self, B: int, HQ: int, D: int, device, group=None, exchange: str = "auto"):
+        import torch.distributed as dist
+
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError(f"exchange must be 'auto', 'peer' or 'nccl', got {exchange!r}")
         self.B, self.HQ, self.D, self.group = B, HQ, D, group
         self.world = dist.get_world_size(group)
         n = wire_floats(B, HQ, D)
@@ -113,6 +185,22 @@ class HistorySplitDecoder:
         self.gathered = torch.empty((self.world, n), device=device, dtype=torch.float32)
         self.out = torch.empty((B, HQ, D), device=device, dtype=torch.float32)
         self.ws: dict = {}
+        self.peer = None
+        self._empty: dict = {}
+        if exchange != "nccl" and self.world <= 8:
+            err = None
+            try:
+                self.peer = PeerExchange(B, HQ, D, device, group)
+            except Exception as exc:  # symmetric memory unavailable on this system
+                err = exc
+            # every rank must take the same path
+            flag = torch.tensor([0 if self.peer is None else 1], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if not bool(flag.item()):
+                self.peer = None
+                if exchange == "peer":
+                    raise RuntimeError(f"peer exchange could not be set up on every rank: {err!r}")
+        self.exchange = "peer" if self.peer is not None else "nccl"
 
     def local_partial(self, q, kq, vq, sm_scale=None):
         """Rank-local unnormalised partial written into the wire buffer."""
@@ -128,13 +216,24 @@ class HistorySplitDecoder:
         return self.local
 
     def step(self, q, kq, vq, sm_scale=None) -> torch.Tensor:
+        if self.peer is not None:
+            from .kernels import fused_decode_attention
+
+            if kq is None or kq.packed.shape[2] == 0:
+                self.peer.push_empty(self._empty, self.out.device)
+            else:
+                fused_decode_attention(q, kq, vq, sm_scale=sm_scale, _workspace=self.ws,
+                                       _partials_only=True, out=self.out)
+                self.peer.push(self.ws["acc"], self.ws["maxs"], self.ws["sums"])
+            return self.peer.wait_merge(self.out)
         self.local_partial(q, kq, vq, sm_scale)
         gather_partials(self.local, self.group, out=self.gathered)
         return merge_gathered(self.gathered, self.B, self.HQ, self.D, out=self.out)
 
 
 def history_split_decode(q, kq, vq, group=None, sm_scale=None) -> torch.Tensor:
-    """One-shot form of :class:`HistorySplitDecoder` (allocates its buffers per call).
-    ``kq``/``vq`` are this rank's slice of the cache (``history_shard`` of the tokens)."""
+    """One-shot form of :class:`HistorySplitDecoder` (allocates its buffers per call, NCCL
+    exchange).  ``kq``/``vq`` are this rank's slice of the cache (``history_shard`` of the
+    tokens)."""
     B, HQ, D = q.shape
-    return HistorySplitDecoder(B, HQ, D, q.device, group).step(q, kq, vq, sm_scale)
+    return HistorySplitDecoder(B, HQ, D, q.device, group, exchange="nccl").step(q, kq, vq, sm_scale)

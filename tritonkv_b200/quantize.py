@@ -210,6 +210,65 @@ def quantize_kv(
     )
 
 
+def empty_cache(B: int, HKV: int, S_cap: int, head_dim: int, nbits: int, group_size: int,
+                device) -> QuantizedTensor:
+    """A zeroed packed cache with room for ``S_cap`` tokens per (sequence, head), to be
+    filled by :func:`append_groupwise`.  No reference counterpart (the reference quantises
+    whole tensors); rows past a sequence's length are never read when ``seq_lens`` is given
+    to the decode functions."""
+    _check_bits(nbits)
+    P = 8 // nbits
+    if group_size <= 0 or head_dim % group_size != 0:
+        raise ValueError(f"group_size {group_size} must divide head_dim {head_dim}")
+    packed = torch.zeros((B, HKV, S_cap, head_dim // P), dtype=torch.uint8, device=device)
+    scale = torch.zeros((B, HKV, S_cap, head_dim // group_size), dtype=torch.float16, device=device)
+    return QuantizedTensor(packed=packed, scale=scale, zero=torch.zeros_like(scale), nbits=nbits,
+                           group_size=group_size, head_dim=head_dim)
+
+
+def append_groupwise(cache: QuantizedTensor, x_new: torch.Tensor, positions) -> QuantizedTensor:
+    """Quantise ``x_new (B, HKV, T_new, D)`` and write it in place into ``cache``
+    ``(B, HKV, S_cap, ...)`` at token rows ``positions[b] + t`` (``positions``: an int for
+    all sequences, or an int32 CUDA tensor ``(B,)``).  One launch, no allocation; the bytes
+    written equal those of :func:`quantize_groupwise` on the same values.  Tokens that would
+    land outside the cache are dropped."""
+    _check_bits(cache.nbits)
+    _cabi.require_cuda(x_new, "x_new")
+    if x_new.dim() != 4 or cache.packed.dim() != 4:
+        raise ValueError("append expects x_new (B, HKV, T_new, D) and a cache (B, HKV, S_cap, ...)")
+    B, HKV, T_new, D = x_new.shape
+    Bc, Hc, S_cap, _ = cache.packed.shape
+    if (B, HKV, D) != (Bc, Hc, cache.head_dim):
+        raise ValueError(f"x_new {tuple(x_new.shape)} does not match the cache {tuple(cache.packed.shape)}")
+    if not (cache.packed.is_contiguous() and cache.scale.is_contiguous() and cache.zero.is_contiguous()):
+        raise ValueError("the cache must be contiguous to be written in place")
+    if x_new.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        x_new = x_new.float()
+    x_new = x_new.contiguous()
+    pos_ptr, pos0 = None, 0
+    if isinstance(positions, torch.Tensor):
+        if positions.dtype != torch.int32 or positions.shape != (B,) or positions.device != x_new.device:
+            raise ValueError("positions must be an int32 tensor of shape (B,) on the cache's device")
+        positions = positions.contiguous()
+        pos_ptr = positions.data_ptr()
+    else:
+        pos0 = int(positions)
+        if pos0 < 0 or pos0 + T_new > S_cap:
+            raise ValueError(f"tokens [{pos0}, {pos0 + T_new}) do not fit a cache of {S_cap} rows")
+    with torch.cuda.device(x_new.device):
+        _cabi.check(_cabi.load().tkv_quantize_append(
+            x_new.data_ptr(), _cabi.dtype_code(x_new), cache.packed.data_ptr(), cache.scale.data_ptr(),
+            cache.zero.data_ptr(), B, HKV, T_new, S_cap, D, cache.nbits, cache.group_size, pos_ptr,
+            pos0, _cabi.stream_ptr(x_new.device)))
+    return cache
+
+
+def append_kv(kq: QuantizedTensor, vq: QuantizedTensor, k_new: torch.Tensor, v_new: torch.Tensor,
+              positions) -> tuple[QuantizedTensor, QuantizedTensor]:
+    """Append new K and V tokens to their caches (see :func:`append_groupwise`)."""
+    return append_groupwise(kq, k_new, positions), append_groupwise(vq, v_new, positions)
+
+
 def roundtrip_error(x: torch.Tensor, nbits: int, group_size: int) -> dict[str, float]:
     """Quantise/dequantise ``x`` and report the reconstruction error."""
     qt = quantize_groupwise(x, nbits, group_size)
