@@ -475,3 +475,26 @@ def test_llama70b_long_context_full_size():
     ref = c_oracle.decode_step(q.float().cpu().numpy(), h(kq.packed), h(kq.scale), h(kq.zero),
                                h(vq.packed), h(vq.scale), h(vq.zero), 2, 32)
     assert_close(got, ref, "llama-70b ctx 131072 2-bit")
+
+
+# ------------------------------------------------------------------ metadata alignment
+@pytest.mark.parametrize("nbits,D,gs", [(4, 128, 128), (2, 64, 64), (4, 128, 64), (2, 128, 32),
+                                        (4, 64, 16)])
+@pytest.mark.parametrize("S", [33, 1001, 2050, 4099])
+def test_scale_zero_rows_at_every_alignment(nbits, D, gs, S):
+    """History lengths that leave the per-sequence scale/zero rows on 2-, 4-, 8- and 16-byte
+    boundaries (one to eight groups per token), dense and ragged, and the same cache seen
+    through a view that starts one sequence in: all copy paths give the oracle's answer."""
+    B, HQ, HKV = 3, 8, 2
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=S + gs)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    ref = oracle_attention(q, kq, vq)
+    assert_close(fused_decode_attention(q, kq, vq), ref, "dense")
+    lens = torch.tensor([S, max(1, S // 3), S - 7], dtype=torch.int32)
+    assert_close(fused_decode_attention(q, kq, vq, seq_lens=lens.to(DEV)),
+                 oracle_attention(q, kq, vq, seq_lens=lens), "ragged")
+    # sequences 1.. of the same storage: the pointers now sit HKV*S rows into the allocation
+    cut = lambda t: Q.QuantizedTensor(t.packed[1:], t.scale[1:], t.zero[1:], nbits, gs, D)
+    if (HKV * S * D * nbits // 8) % 16 == 0:  # the packed codes themselves need 16-byte alignment
+        got = fused_decode_attention(q[1:].contiguous(), cut(kq), cut(vq))
+        assert_close(got, ref[1:], "offset view")

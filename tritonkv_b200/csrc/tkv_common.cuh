@@ -47,6 +47,19 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int sr
                "r"(src_bytes)
                : "memory");
 }
+// 4-, 8- or 16-byte asynchronous copy (the small sizes only exist with .ca); bytes past
+// `src_bytes` are zero-filled.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_n(uint32_t dst, const void* src, int src_bytes) {
+  static_assert(BYTES == 4 || BYTES == 8 || BYTES == 16, "cp.async copies 4, 8 or 16 bytes");
+  if constexpr (BYTES == 16) {
+    cp_async16(dst, src, src_bytes);
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;\n" ::"r"(dst), "l"(src), "n"(BYTES),
+                 "r"(src_bytes)
+                 : "memory");
+  }
+}
 __device__ __forceinline__ void cp_async_commit() {
   asm volatile("cp.async.commit_group;\n" ::: "memory");
 }

@@ -62,7 +62,13 @@ struct FusedCfg {
   static constexpr int CODE_BYTES = (kTok * DP + 1023) / 1024 * 1024;  // keeps V's swizzle phase
   static constexpr int NPAIR = (NBLK + 1) / 2;  // ldmatrix issues per 16-token half
   static constexpr int META_BYTES = kTok * NG * 2;
-  static constexpr int PAYLOAD = 2 * CODE_BYTES + 4 * META_BYTES;
+  // Distance between the four metadata arrays of a stage.  With one group per token a row
+  // is 2 bytes and a tile may start 2 bytes off a 4-byte boundary: such tiles are copied
+  // from the boundary below (one 4-byte copy more) and read back at a 2-byte shift, which
+  // is kept in the word after the arrays.
+  static constexpr int META_STRIDE = (NG == 1) ? META_BYTES + 16 : META_BYTES;
+  static constexpr int SHIFT_WORD = 4 * META_STRIDE;  // byte offset inside the metadata area
+  static constexpr int PAYLOAD = 2 * CODE_BYTES + 4 * META_STRIDE + (NG == 1 ? 16 : 0);
   static constexpr int MERGE_BYTES = kHeadsPerCta * D * 4;  // one warp's partial in the epilogue
   static constexpr int STAGE_BYTES =
       ((PAYLOAD > MERGE_BYTES ? PAYLOAD : MERGE_BYTES) + 1023) / 1024 * 1024;  // keeps swizzle atoms aligned
@@ -197,7 +203,11 @@ struct FusedPolicy {
     // ~100+ cycles each, four of them per tile were a third of the loop time); every lane
     // then posts one arrival on the stage barrier that fires when its copies have landed.
     const uint32_t mst = st + 2 * C::CODE_BYTES;
-    if (p.meta_aligned && nvalid == kTok) {
+    if (NG == 1 && lane == 0)  // this tile's read-back shift (nonzero only on the path at the end)
+      asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(mst + C::SHIFT_WORD),
+                   "r"(p.meta_aligned == 0 ? (uint32_t)((p.meta_phase + row * 2) & 3) : 0u)
+                   : "memory");
+    if (NG > 1 && p.meta_aligned == 16 && nvalid == kTok) {
       const int64_t off = (int64_t)row * (NG * 2);  // bytes
 #pragma unroll
       for (int r = 0; r < ROUNDS; ++r) {
@@ -205,20 +215,52 @@ struct FusedPolicy {
           cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + off, 16);
       }
       cp_async_mbar_arrive_noinc(bar);
+    } else if (p.meta_aligned == 16) {
+      issue_meta<16>(p, row, nvalid, mst, bar, lane);
+    } else if (p.meta_aligned == 8) {
+      issue_meta<8>(p, row, nvalid, mst, bar, lane);
+    } else if (p.meta_aligned == 4) {
+      issue_meta<4>(p, row, nvalid, mst, bar, lane);
     } else {
-      // ragged tail or unaligned rows: plain loads; tokens past the end get scale = zero = 0
-      __half* dstm = reinterpret_cast<__half*>(st_ptr + 2 * C::CODE_BYTES);
-      const int64_t off = (int64_t)row * NG;
-      const __half zero = __float2half(0.f);
-      for (int i = lane; i < kTok * NG; i += 32) {
-        const bool ok = (i / NG) < nvalid;
-        dstm[i] = ok ? p.ks[off + i] : zero;
-        dstm[kTok * NG + i] = ok ? p.kz[off + i] : zero;
-        dstm[2 * kTok * NG + i] = ok ? p.vs[off + i] : zero;
-        dstm[3 * kTok * NG + i] = ok ? p.vz[off + i] : zero;
+      // one group per row and an odd history length: rows are aligned to 2 bytes only.
+      // Copy from the 4-byte boundary below and let the reader skip the first 2 bytes.
+      const int shift = (p.meta_phase + row * 2) & 3;  // 0 or 2
+      constexpr int N = C::META_BYTES / 4 + 1;  // 4-byte copies per array
+      const int vbytes = nvalid * NG * 2 + shift;
+      const int64_t off = (int64_t)row * (NG * 2) - shift;
+      for (int i = lane; i < 4 * N; i += 32) {
+        const int arr = i / N, c = i - arr * N;
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(
+            arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz);
+        const int nb = min(max(vbytes - c * 4, 0), 4);
+        cp_async_n<4>(mst + arr * C::META_STRIDE + c * 4, nb > 0 ? base + off + c * 4 : base - p.meta_phase,
+                      nb);
       }
-      mbar_arrive(bar);
+      cp_async_mbar_arrive_noinc(bar);
     }
+  }
+
+  // Scale/zero of a tile in CS-byte copies: rows that only start on 8- or 4-byte boundaries
+  // (odd history lengths), and the last tile of a unit, whose tokens past the end are
+  // zero-filled by the copy itself (scale = zero = 0 makes them contribute exact zeros).
+  template <int CS>
+  __device__ static __forceinline__ void issue_meta(const DecodeParams& p, int row, int nvalid,
+                                                    uint32_t mst, uint32_t bar, int lane) {
+    constexpr int N = C::META_BYTES / CS;  // copies per array
+    const int vbytes = nvalid * NG * 2;    // valid bytes of each array in this tile
+    const int64_t off = (int64_t)row * (NG * 2);
+#pragma unroll
+    for (int i0 = 0; i0 < 4 * N; i0 += 32) {
+      const int i = i0 + lane;
+      if (4 * N >= 32 || i < 4 * N) {
+        const int arr = (i / N) & 3, c = i % N;
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(
+            arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz);
+        const int nb = min(max(vbytes - c * CS, 0), CS);
+        cp_async_n<CS>(mst + arr * C::META_STRIDE + c * CS, nb > 0 ? base + off + c * CS : base, nb);
+      }
+    }
+    cp_async_mbar_arrive_noinc(bar);
   }
 
   // Lane constants of the tile loop: set once per warp.
@@ -357,8 +399,10 @@ struct FusedPolicy {
                                                 int lane) {
     const int g = lane >> 2;
     const uint32_t kc = st;
-    const uint32_t ks_a = st + 2 * C::CODE_BYTES + qq.o_row;
-    const uint32_t kz_a = st + 2 * C::CODE_BYTES + C::META_BYTES + qq.o_kz;
+    uint32_t ms = st + 2 * C::CODE_BYTES;
+    if constexpr (NG == 1) ms += lds_u32(ms + C::SHIFT_WORD);  // 0 or 2, see FusedCfg::META_STRIDE
+    const uint32_t ks_a = ms + qq.o_row;
+    const uint32_t kz_a = ms + C::META_STRIDE + qq.o_kz;
     const float qk24 = qk_scale * 16777216.f;  // the code fields carry 2^-24
     constexpr int HALF = 16 * NG * 2;           // bytes of 16 token rows in a metadata array
 
@@ -454,8 +498,10 @@ struct FusedPolicy {
   __device__ static __forceinline__ void update(Accum& ac, const Query& qq, Scores& in,
                                                 uint32_t st, uint8_t*, int left, int lane) {
     const uint32_t vc = st + C::CODE_BYTES;
-    const uint32_t vs_a = st + 2 * C::CODE_BYTES + 2 * C::META_BYTES + qq.o_row;
-    const uint32_t vz_a = st + 2 * C::CODE_BYTES + 3 * C::META_BYTES + qq.o_vz;
+    uint32_t ms = st + 2 * C::CODE_BYTES;
+    if constexpr (NG == 1) ms += lds_u32(ms + C::SHIFT_WORD);
+    const uint32_t vs_a = ms + 2 * C::META_STRIDE + qq.o_row;
+    const uint32_t vz_a = ms + 3 * C::META_STRIDE + qq.o_vz;
     constexpr int HALF = 16 * NG * 2;
     float (&sc)[2][4] = in.s;
     // ---- online softmax with a lazily raised reference exponent ----
@@ -691,10 +737,25 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
   p.vs = (const __half*)v_scale;
   p.vz = (const __half*)v_zero;
   const int ng = (gs > 0 && D % gs == 0) ? D / gs : 0;
-  p.meta_aligned = (ng > 0 && ((int64_t)S * ng * 2) % 16 == 0 && aligned16(k_scale) &&
-                    aligned16(k_zero) && aligned16(v_scale) && aligned16(v_zero))
-                       ? 1
-                       : 0;
+  // Alignment of the first byte of any scale/zero tile: the pointers' own alignment, that
+  // of a sequence's stride when there is more than one, and 32 bytes inside a sequence
+  // (tiles start at multiples of 16 tokens).  The copies use the largest unit that fits.
+  {
+    const int res = (int)(reinterpret_cast<uintptr_t>(k_scale) & 15);
+    TKV_REQUIRE((int)(reinterpret_cast<uintptr_t>(k_zero) & 15) == res &&
+                    (int)(reinterpret_cast<uintptr_t>(v_scale) & 15) == res &&
+                    (int)(reinterpret_cast<uintptr_t>(v_zero) & 15) == res && (res & 1) == 0,
+                TKV_ERR_ALIGN,
+                "fused decode: the four scale/zero pointers must share their offset within 16 bytes");
+    const int64_t seq_bytes = (int64_t)S * ng * 2;
+    const int ptr_al = (res | 16) & -(res | 16);
+    const int seq_al = ((int64_t)B * HKV > 1) ? (int)((seq_bytes | 16) & -(seq_bytes | 16)) : 16;
+    const int al = ptr_al < seq_al ? ptr_al : seq_al;
+    p.meta_aligned = al >= 4 ? al : 0;
+    p.meta_phase = res & 3;
+    TKV_REQUIRE(al >= 4 || ng == 1, TKV_ERR_ALIGN,
+                "fused decode: scale/zero rows of %d bytes must start on 4-byte boundaries", ng * 2);
+  }
   // 128-byte-row view of the code tensors: every sequence must start on a 128-byte boundary
   p.wide = (((int64_t)S * D * nbits / 8) % 128 == 0) ? 1 : 0;
   SplitSched sc;

@@ -36,7 +36,8 @@ struct DecodeParams {
   int split_size;  // tokens per split, multiple of 16
   float qk_scale;  // sm_scale * log2(e)
   int partials;    // 1: write (acc, m, l); 0: write normalised out
-  int meta_aligned;  // 1: scale/zero tiles start on 16-byte boundaries (cp.async path)
+  int meta_aligned;  // bytes every scale/zero tile start is aligned to: 16, 8, 4, or 0 (2 bytes only)
+  int meta_phase;    // with meta_aligned == 0: the scale/zero pointers modulo 4 (0 or 2)
   int wide;          // 1: code tensors are fetched as 128-byte rows (128B TMA swizzle)
 };
 
