@@ -29,11 +29,14 @@
 
 namespace tkv {
 
+constexpr int kMaxRaggedB = 512;  // sequences whose tile prefix fits the kernel's static shared memory
 constexpr float kLazyTau = 4.0f;  // head-room of the lazily raised softmax exponent (log2 units)
 
 struct SplitSched {
-  int persistent;  // 0: CTA c <-> unit c (ragged batches); 1: balanced tile ranges over the
-                   // global tile sequence; 2: SEG CTAs per unit, ranges aligned to the unit
+  int persistent;  // 0: CTA c <-> unit c (ragged batches with explicit splits); 1: balanced
+                   // tile ranges over the global tile sequence; 2: SEG CTAs per unit, ranges
+                   // aligned to the unit; 3: balanced ranges over a ragged batch, the tile
+                   // sequence built on the device from seq_lens
   int NS;          // history splits per sequence (unit boundaries)
   int TUf, TUl;    // tiles in a full split / in the last split
   int T_seq;       // tiles per sequence = (NS-1)*TUf + TUl
@@ -56,7 +59,18 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
   if (num_splits == 1) s.TUf = s.TUl;
   s.T_seq = (num_splits - 1) * s.TUf + s.TUl;
   const int64_t units = (int64_t)B * s.HKVc * num_splits;
-  if (ragged) {
+  if (ragged && num_splits == 1 && B <= kMaxRaggedB) {
+    // Lengths live on the device, so only bounds are known here: one wave of CTAs, and
+    // per unit at most min(tiles, wave/HKVc + 2) segments (a unit of t tiles is cut into
+    // at most t/TC + 2 ranges and TC >= HKVc * t / wave).
+    s.persistent = 3;
+    s.T = 0;
+    s.TC = 0;
+    s.grid = wave;
+    const int by_wave = wave / s.HKVc + 2;
+    s.SEG = s.TUf < by_wave ? s.TUf : by_wave;
+    if (s.SEG < 1) s.SEG = 1;
+  } else if (ragged) {
     s.persistent = 0;
     s.T = 0;
     s.TC = 0;
@@ -139,6 +153,44 @@ __device__ __forceinline__ Segment segment_at(const DecodeParams& p, const Split
   return s;
 }
 
+// Ragged batches: `pref[b]` = tiles of sequences 0..b-1 (one KV head), so unit
+// (b, hk) starts at global tile HKVc*pref[b] + hk*t_b with t_b = pref[b+1] - pref[b].
+template <int kTok>
+__device__ __forceinline__ Segment ragged_segment_at(const DecodeParams& p, const SplitSched& sc,
+                                                     const int* pref, int TC, int g, int g1,
+                                                     int cta) {
+  Segment s;
+  int lo = 0, hi = p.B;  // largest b with HKVc*pref[b] <= g (sequences without tiles are skipped)
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sc.HKVc * pref[mid] <= g) lo = mid; else hi = mid;
+  }
+  const int b = lo;
+  const int t_b = pref[b + 1] - pref[b];
+  const int r = g - sc.HKVc * pref[b];
+  const int hk = r / t_b;
+  const int tile = r - hk * t_b;
+  const int unit_start = g - tile, unit_end = unit_start + t_b;
+  s.b = b;
+  s.hkv = hk / p.hchunks;
+  s.hc = hk - s.hkv * p.hchunks;
+  s.split = 0;
+  s.hi = min(max(p.seq_lens[b], 0), p.S);
+  s.lo_tok = tile * kTok;
+  s.g_end = min(g1, unit_end);
+  s.ntiles = s.g_end - g;
+  const int seg = cta - unit_start / TC;
+  s.slot = seg;
+  if (s.g_end == unit_end && seg + 1 < sc.SEG) {
+    s.fill_from = seg + 1;
+    s.fill_to = sc.SEG;
+  } else {
+    s.fill_from = -1;
+    s.fill_to = -1;
+  }
+  return s;
+}
+
 // Per-warp cursor over the tiles this warp will issue, possibly segments ahead.
 struct IssueCursor {
   int seg_g;      // global tile index where the cursor's segment starts (persistent mode)
@@ -186,6 +238,8 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   uint8_t* qbuf = reinterpret_cast<uint8_t*>(qbars + 2);
   const uint32_t qbuf_u32 = smem_u32(qbuf);
   const uint32_t qfrag_u32 = qbuf_u32 + 2 * QB;  // query fragments shared by the warps
+  // ragged batches only (the launch adds the bytes): tiles before each sequence
+  int* s_pref = reinterpret_cast<int*>(qbuf + 2 * QB + ((Policy::QFRAG_BYTES + 15) & ~15));
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(bar_u32 + 8 * s, Policy::BAR_COUNT);
@@ -212,12 +266,67 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
 
   // ---- this CTA's tile range ----
   int g0, g1;
+  int TC = sc.TC;  // tiles per CTA (computed here for ragged batches)
   Segment seg;
+  auto seg_at = [&](int g, int g_hi) {
+    return sc.persistent == 3 ? ragged_segment_at<kTok>(p, sc, s_pref, TC, g, g_hi, cta)
+                              : segment_at<kTok>(p, sc, g, g_hi, cta);
+  };
   if (sc.persistent == 1) {
     g0 = min(cta * sc.TC, sc.T);
     g1 = min(g0 + sc.TC, sc.T);
     if (g0 >= g1) return;
     seg = segment_at<kTok>(p, sc, g0, g1, cta);
+  } else if (sc.persistent == 3) {
+    // balanced ranges over a ragged batch: every CTA builds the tile prefix of the
+    // sequences (warp 0, 32 at a time), then cuts the global tile sequence evenly
+    pdl_wait();
+    if (warp == 0) {
+      int carry = 0;
+      for (int b0 = 0; b0 < p.B; b0 += 32) {
+        const int b = b0 + lane;
+        const int len = b < p.B ? min(max(p.seq_lens[b], 0), p.S) : 0;
+        int t = (len + kTok - 1) / kTok, incl = t;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int y = __shfl_up_sync(kFullMask, incl, off);
+          if (lane >= off) incl += y;
+        }
+        if (b < p.B) s_pref[b] = carry + incl - t;
+        carry += __shfl_sync(kFullMask, incl, 31);
+      }
+      if (lane == 0) s_pref[p.B] = carry;
+    }
+    __syncthreads();
+    const int T = sc.HKVc * s_pref[p.B];
+    TC = max(1, (T + (int)gridDim.x - 1) / (int)gridDim.x);
+    // units without tokens are touched by no range: their slots are marked empty here
+    for (int u = cta; u < p.B * sc.HKVc; u += gridDim.x) {
+      const int b = u / sc.HKVc, hk = u - b * sc.HKVc;
+      if (s_pref[b + 1] == s_pref[b] && p.partials) {
+        const int hkv = hk / p.hchunks, hc = hk - hkv * p.hchunks;
+        for (int idx = threadIdx.x; idx < kHeadsPerCta * sc.SEG; idx += WARPS * 32) {
+          const int h = idx / sc.SEG, j = idx - h * sc.SEG;
+          const int hg = hc * kHeadsPerCta + h;
+          if (hg < p.group) {
+            const int64_t hq = (int64_t)b * p.HQ + hkv * p.group + hg;
+            p.m[hq * sc.nslots + j] = -INFINITY;
+            p.l[hq * sc.nslots + j] = 0.f;
+          }
+        }
+      } else if (s_pref[b + 1] == s_pref[b]) {
+        for (int idx = threadIdx.x; idx < kHeadsPerCta * D; idx += WARPS * 32) {
+          const int h = idx / D, d = idx - h * D;
+          const int hkv = hk / p.hchunks, hc = hk - hkv * p.hchunks;
+          const int hg = hc * kHeadsPerCta + h;
+          if (hg < p.group) p.out[((int64_t)b * p.HQ + hkv * p.group + hg) * D + d] = 0.f;
+        }
+      }
+    }
+    g0 = min(cta * TC, T);
+    g1 = min(g0 + TC, T);
+    if (g0 >= g1) return;
+    seg = seg_at(g0, g1);
   } else if (sc.persistent == 2) {
     // unit-aligned: CTA j of the unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG) of the unit
     const int u = cta / sc.SEG, j = cta - u * sc.SEG;
@@ -289,9 +398,9 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   cursor_enter(cur, seg, g0);
   auto cursor_skip_empty = [&]() {
     // move to the next segment in which this warp has a tile (persistent mode only)
-    while (cur.cnt == 0 && sc.persistent == 1 && cur.g_end < g1) {
+    while (cur.cnt == 0 && (sc.persistent & 1) && cur.g_end < g1) {
       const int g = cur.g_end;
-      const Segment s = segment_at<kTok>(p, sc, g, g1, cta);
+      const Segment s = seg_at(g, g1);
       cursor_enter(cur, s, g);
     }
   };
@@ -326,8 +435,8 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   prefetch_q(0, seg.b, seg.hkv, seg.hc);
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue_next();
-  if (sc.persistent == 1 && seg.g_end < g1) {
-    const Segment s1 = segment_at<kTok>(p, sc, seg.g_end, g1, cta);
+  if ((sc.persistent & 1) && seg.g_end < g1) {
+    const Segment s1 = seg_at(seg.g_end, g1);
     prefetch_q(1, s1.b, s1.hkv, s1.hc);
   }
   int seg_k = 0;  // index of the current segment within this CTA
@@ -474,12 +583,12 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     __syncthreads();
     need_proxy_fence = true;
 
-    if (sc.persistent != 1) break;
+    if (!(sc.persistent & 1)) break;
     g = seg.g_end;
     if (g >= g1 || timed_out) break;
-    seg = segment_at<kTok>(p, sc, g, g1, cta);
+    seg = seg_at(g, g1);
     if (seg.g_end < g1) {  // the query slot just released takes the segment after the next
-      const Segment s2 = segment_at<kTok>(p, sc, seg.g_end, g1, cta);
+      const Segment s2 = seg_at(seg.g_end, g1);
       prefetch_q(seg_k & 1, s2.b, s2.hkv, s2.hc);
     }
     ++seg_k;
@@ -538,13 +647,15 @@ struct SplitLaunch {
            Policy::QFRAG_BYTES +                    // query fragments shared by the warps
            1024;                                    // slack for the 1024-byte alignment of the ring
   }
+  static constexpr int kPrefixBytes = (kMaxRaggedB + 1) * 4 + 32;  // ragged batches: tile prefix
   static const void* fn() { return reinterpret_cast<const void*>(&splitk_kernel<Policy>); }
   static int prepare() {
     static bool done[64] = {};
     int dev = 0;
     TKV_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && done[dev]) return TKV_OK;
-    TKV_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    TKV_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  smem_bytes() + kPrefixBytes));
     if (dev < 64) done[dev] = true;
     return TKV_OK;
   }
@@ -591,7 +702,8 @@ struct SplitLaunch {
       TKV_CUDA(launch_pdl(splitk_kernel<Policy>, dim3(sc.grid), dim3(Policy::WARPS * 32),
                           (size_t)smem_bytes(), stream, maps, p, sc));
     } else {
-      splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem_bytes(), stream>>>(maps, p, sc);
+      const int smem = smem_bytes() + (sc.persistent == 3 ? kPrefixBytes : 0);
+      splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem, stream>>>(maps, p, sc);
       TKV_CUDA(cudaGetLastError());
     }
     return TKV_OK;

@@ -61,6 +61,9 @@ def balanced_num_splits(B: int, HKV: int, n_blocks: int, block_n: int, wave: int
     return best
 
 
+MAX_BALANCED_RAGGED_BATCH = 512  # kMaxRaggedB of the kernels: sequences per device-built schedule
+
+
 def split_geometry(S: int, block_n: int, num_splits: int | None, B: int, HKV: int,
                    target_programs: int | None, ragged: bool = False):
     """(block_n, num_splits, split_size) with the reference's clamping
@@ -68,17 +71,19 @@ def split_geometry(S: int, block_n: int, num_splits: int | None, B: int, HKV: in
     splits are whole multiples of block_n and none is empty.
 
     ``num_splits=None``: the kernels balance the work themselves (every CTA gets an
-    equal contiguous range of tiles, see ``tkv_decode_plan``), so one split covering
-    the whole history is requested -- except for ragged batches (``seq_lens``), which
-    are scheduled one CTA per (sequence, KV head, split) and therefore get a split
-    count from the cost model, given ``target_programs`` CTAs resident at once.
+    equal contiguous range of tiles, see ``tkv_decode_plan``; for ragged batches the
+    tile sequence is built on the device from ``seq_lens``), so one split covering the
+    whole history is requested -- except for ragged batches of more than
+    ``MAX_BALANCED_RAGGED_BATCH`` sequences, which are scheduled one CTA per (sequence,
+    KV head, split) and get a split count from the cost model, given ``target_programs``
+    CTAs resident at once.
     """
     block_n = min(block_n, max(16, next_pow2(S)))
     if block_n < 16 or block_n % 16:
         raise ValueError(f"block_n must be a multiple of 16, got {block_n}")
     n_blocks = cdiv(S, block_n)
     if num_splits is None:
-        if not ragged:
+        if not ragged or B <= MAX_BALANCED_RAGGED_BATCH:
             num_splits = 1
         elif target_programs is None:
             num_splits = pick_num_splits(B, HKV, n_blocks, None)
