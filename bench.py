@@ -2,7 +2,7 @@
 """Benchmark of the packed-KV decode-attention path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload qwen-b1|llama8b-b64|llama70b-128k] [--nbits 4|2] [--ctx N]
+                    [--workload qwen-b1|llama8b-b64|llama70b-128k|ragged-b16] [--nbits 4|2] [--ctx N]
 
 One "step" is one decode step: one call of ``fused_decode_attention`` over the whole
 cache of the workload.  The metric is the algorithmic HBM bandwidth of that step
@@ -42,6 +42,9 @@ WORKLOADS = {
     "qwen-b1": (1, 12, 2, 128, 65536, 4, "Qwen2.5-1.5B attention shape, batch 1"),
     "llama8b-b64": (64, 32, 8, 128, 4096, 4, "Llama-3-8B shape, batch 64, ctx 4096"),
     "llama70b-128k": (1, 64, 8, 128, 131072, 2, "Llama-3-70B shape, batch 1, ctx 131072"),
+    # ragged batch: per-sequence lengths uniform in [1024, ctx] from the seed; bytes counted
+    # are those of the valid tokens only
+    "ragged-b16": (16, 32, 8, 128, 32768, 4, "ragged batch 16, lengths uniform in [1024, 32768]"),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the split kernel from the
@@ -255,7 +258,16 @@ def run_ours(args):
 
     sampler = harness.ClockSampler(local).start()
 
+    seq_lens = None
+    if args.workload == "ragged-b16":
+        from tritonkv_b200.workloads import ragged_seq_lens
+        lens = ragged_seq_lens(B, 1024, ctx, seed=args.seed + rank)
+        S_local = int(lens.max())
+        seq_lens = lens.to(device)
+        valid_tokens = int(lens.sum())
     cbytes = fused_bytes(B, HKV, S_local, D, nbits)
+    if seq_lens is not None:  # only the valid tokens are read
+        cbytes = cbytes * valid_tokens // (B * S_local)
     R = max(2, harness.replicas_for(cbytes, l2))
     cbytes16 = fp16_bytes(B, HKV, S_local, D)
     R16 = max(2, harness.replicas_for(cbytes16, l2)) if not args.no_table else 0
@@ -294,7 +306,8 @@ def run_ours(args):
     else:
         def make_step(i):
             r = reps[i]
-            return lambda: fused_decode_attention(r["q"], r["kq"], r["vq"], out=outs[i], _workspace=ws)
+            return lambda: fused_decode_attention(r["q"], r["kq"], r["vq"], out=outs[i], _workspace=ws,
+                                                  seq_lens=seq_lens)
         launches_per_step = None  # filled below from the geometry
 
     steps = [make_step(i) for i in range(R)]
@@ -337,7 +350,7 @@ def run_ours(args):
         run_direct(W)
         ms = harness.time_region(lambda: run_direct(K), barrier)
     ms = max_over_ranks(ms)
-    total_bytes = fused_bytes(B, HKV, S_local, D, nbits) * world  # all ranks' caches
+    total_bytes = cbytes * world  # all ranks' caches
     value = total_bytes * K / (ms * 1e-3) / 1e9
 
     # ---- roofline of the dominant kernel: the split kernel alone, same geometry ----
@@ -347,7 +360,8 @@ def run_ours(args):
         def make_split(i):
             r = reps[i]
             return lambda: fused_decode_attention(r["q"], r["kq"], r["vq"], out=outs[i],
-                                                  _workspace=ws2, _partials_only=True)
+                                                  _workspace=ws2, _partials_only=True,
+                                                  seq_lens=seq_lens)
         sp = [make_split(i) for i in range(R)]
         sgs = harness.StepGraphs(sp, K)
         sgs.run()
@@ -373,7 +387,8 @@ def run_ours(args):
         for i in range(n):
             r = reps[i % R]
             q_dev.copy_(q_host[i % R], non_blocking=True)
-            fused_decode_attention(q_dev, r["kq"], r["vq"], out=outs[0], _workspace=ws)
+            fused_decode_attention(q_dev, r["kq"], r["vq"], out=outs[0], _workspace=ws,
+                                   seq_lens=seq_lens)
             out_host.copy_(outs[0], non_blocking=True)
             stream.synchronize()  # the host reads this step's result before the next one
 
