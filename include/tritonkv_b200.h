@@ -42,6 +42,7 @@ extern "C" {
 
 /* flags for the two decode entry points */
 #define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when nslots == 1 */
+#define TKV_FLAG_COMBINE 2       /* with nslots > 1: enqueue tkv_combine(acc, m, l -> out) after the split kernel */
 
 /* kernel ids for tkv_kernel_attrs */
 #define TKV_KERNEL_FUSED_SPLIT 0
@@ -102,7 +103,8 @@ int tkv_decode_plan(int kernel_id, int nbits, int D, int gs, int B, int HQ, int 
  * group.  Split s covers tokens [s*split_size, min((s+1)*split_size, S_b)).  With
  * nslots == 1 (from tkv_decode_plan) and no TKV_FLAG_PARTIALS_ONLY the normalised result
  * goes to `out` and acc/m/l may be null; otherwise partials go to acc (B,HQ,nslots,D),
- * m, l (B,HQ,nslots) and `out` is untouched (call tkv_combine with NS = nslots next).
+ * m, l (B,HQ,nslots) and `out` is untouched (call tkv_combine with NS = nslots next, or
+ * pass TKV_FLAG_COMBINE to have it enqueued by the same call).
  * seq_lens (B,) int32 device pointer or null: per-sequence history length S_b <= S (no
  * reference counterpart; null == S). */
 int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_packed, const void* k_scale,

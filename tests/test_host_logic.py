@@ -92,3 +92,25 @@ def test_product_never_imports_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f
                 assert "tkv_oracle" not in text, f
+
+
+def test_ragged_batches_ask_for_one_split_up_to_the_device_schedule_limit():
+    """Ragged batches are balanced by the kernel from seq_lens (one split requested) up to
+    MAX_BALANCED_RAGGED_BATCH sequences; above it the static schedule gets a split count
+    from the cost model."""
+    lim = _launch.MAX_BALANCED_RAGGED_BATCH
+    assert _launch.split_geometry(20000, 64, None, 16, 8, 444, ragged=True)[1] == 1
+    assert _launch.split_geometry(20000, 64, None, lim, 8, 444, ragged=True)[1] == 1
+    assert _launch.split_geometry(20000, 64, None, lim + 1, 1, 444, ragged=True)[1] >= 1
+    # an explicit split count is always honoured
+    assert _launch.split_geometry(20000, 64, 5, 16, 8, 444, ragged=True)[1] == 5
+
+
+def test_peer_exchange_layout():
+    from tritonkv_b200 import parallel as P
+
+    wire = P.wire_floats(1, 64, 128)
+    state_off, total = P.exchange_layout(8, wire)
+    assert state_off == 2 * 8 * wire * 8          # two parities x world blocks of 8-byte pairs
+    assert total == state_off + 16 and total % 16 == 0 and state_off % 16 == 0
+    assert wire % 4 == 0 and wire >= 64 * (128 + 2)

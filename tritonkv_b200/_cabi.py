@@ -24,6 +24,7 @@ TKV_ERR_ALIGN = 4
 
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 FLAG_PARTIALS_ONLY = 1
+FLAG_COMBINE = 2
 KERNEL_FUSED_SPLIT, KERNEL_FP16_SPLIT = 0, 1
 
 _TORCH_DTYPE = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32}
@@ -148,8 +149,18 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
         )
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device: torch.device) -> int:
+    """Handle of torch's current stream on ``device`` (the raw getter when torch has it:
+    the Stream object costs microseconds per call)."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+_current_device = getattr(torch._C, "_cuda_getDevice", None) or torch.cuda.current_device
 
 
 class on_device:
@@ -159,11 +170,11 @@ class on_device:
     __slots__ = ("idx", "prev")
 
     def __init__(self, device: torch.device):
-        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.idx = device.index if device.index is not None else _current_device()
         self.prev = -1
 
     def __enter__(self):
-        cur = torch.cuda.current_device()
+        cur = _current_device()
         if cur != self.idx:
             self.prev = cur
             torch.cuda.set_device(self.idx)
@@ -211,7 +222,7 @@ def decode_plan(kernel_id: int, nbits: int, D: int, gs: int, B: int, HQ: int, HK
                 num_splits: int, split_size: int, ragged: bool) -> tuple[int, int]:
     """(nslots, grid): partial slots per (batch, head) and CTAs of the split kernel."""
     key = (kernel_id, nbits, D, gs, B, HQ, HKV, S, num_splits, split_size, ragged,
-           torch.cuda.current_device())
+           _current_device())
     r = _plan_cache.get(key)
     if r is None:
         ns, grid = c_int(0), c_int(0)

@@ -277,7 +277,13 @@ extern "C" int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const 
   TKV_REQUIRE(sc.nslots == nslots, TKV_ERR_INVALID,
               "fp16 decode: nslots=%d does not match the plan (%d); size acc/m/l with "
               "tkv_decode_plan", nslots, sc.nslots);
-  if (D == 128) return fp16_launch_one<128>(p, sc, (cudaStream_t)stream);
-  if (D == 64) return fp16_launch_one<64>(p, sc, (cudaStream_t)stream);
-  return fp16_unsupported(D);
+  if (D == 128) rc = fp16_launch_one<128>(p, sc, (cudaStream_t)stream);
+  else if (D == 64) rc = fp16_launch_one<64>(p, sc, (cudaStream_t)stream);
+  else return fp16_unsupported(D);
+  if (rc != TKV_OK) return rc;
+  if ((flags & TKV_FLAG_COMBINE) && nslots > 1 && !(flags & TKV_FLAG_PARTIALS_ONLY)) {
+    TKV_REQUIRE(out, TKV_ERR_INVALID, "fp16 decode: TKV_FLAG_COMBINE needs out");
+    return tkv_combine(acc, m, l, out, nullptr, nullptr, B, HQ, nslots, D, stream);
+  }
+  return TKV_OK;
 }

@@ -765,5 +765,11 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
   TKV_REQUIRE(sc.nslots == nslots, TKV_ERR_INVALID,
               "fused decode: nslots=%d does not match the plan (%d); size acc/m/l with "
               "tkv_decode_plan", nslots, sc.nslots);
-  return fused_launch(nbits, D, gs, p, sc, (cudaStream_t)stream);
+  rc = fused_launch(nbits, D, gs, p, sc, (cudaStream_t)stream);
+  if (rc != TKV_OK) return rc;
+  if ((flags & TKV_FLAG_COMBINE) && nslots > 1 && !(flags & TKV_FLAG_PARTIALS_ONLY)) {
+    TKV_REQUIRE(out, TKV_ERR_INVALID, "fused decode: TKV_FLAG_COMBINE needs out");
+    return tkv_combine(acc, m, l, out, nullptr, nullptr, B, HQ, nslots, D, stream);
+  }
+  return TKV_OK;
 }

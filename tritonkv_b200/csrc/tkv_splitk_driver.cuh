@@ -621,6 +621,24 @@ inline EncodeTiledFn encode_tiled_fn() {
 // shared-memory swizzle that makes 8-row x 16-byte ldmatrix blocks conflict free.
 inline int make_row_map(CUtensorMap* tm, const void* base, int64_t rows, int row_bytes,
                         int box_bytes, int box_rows) {
+  // A decode loop encodes the same few maps every step: keep the last ones per thread.
+  struct Entry {
+    const void* base;
+    int64_t rows;
+    int row_bytes, box_bytes, box_rows;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 8;
+  thread_local Entry cache[kEntries] = {};
+  thread_local int next = 0;
+  for (int i = 0; i < kEntries; ++i) {
+    const Entry& e = cache[i];
+    if (e.base == base && e.rows == rows && e.row_bytes == row_bytes && e.box_bytes == box_bytes &&
+        e.box_rows == box_rows) {
+      *tm = e.map;
+      return TKV_OK;
+    }
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   TKV_REQUIRE(fn != nullptr, TKV_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
   const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
@@ -636,6 +654,14 @@ inline int make_row_map(CUtensorMap* tm, const void* base, int64_t rows, int row
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TKV_REQUIRE(r == CUDA_SUCCESS, TKV_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
               (int)r);
+  Entry& e = cache[next];
+  next = (next + 1) % kEntries;
+  e.base = base;
+  e.rows = rows;
+  e.row_bytes = row_bytes;
+  e.box_bytes = box_bytes;
+  e.box_rows = box_rows;
+  e.map = *tm;
   return TKV_OK;
 }
 

@@ -73,13 +73,11 @@ def fp16_decode_attention(
         acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
 
         stream = _cabi.stream_ptr(device)
-        flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else 0
+        # one call enqueues the split kernel and, when there are partials to merge, the combine
+        flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else _cabi.FLAG_COMBINE
         _cabi.check(lib.tkv_fp16_decode(
             q.data_ptr(), _cabi.dtype_code(q), k.data_ptr(), v.data_ptr(),
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
             B, HQ, HKV, S, D, float(sm_scale), num_splits, split_size, nslots,
             _cabi.ptr(seq_lens), flags, stream))
-        if acc is not None and not _partials_only:
-            _cabi.check(lib.tkv_combine(acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(),
-                                        out.data_ptr(), None, None, B, HQ, nslots, D, stream))
     return out

@@ -119,7 +119,8 @@ def fused_decode_attention(
         acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
 
         stream = _cabi.stream_ptr(device)
-        flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else 0
+        # one call enqueues the split kernel and, when there are partials to merge, the combine
+        flags = _cabi.FLAG_PARTIALS_ONLY if _partials_only else _cabi.FLAG_COMBINE
         _cabi.check(lib.tkv_fused_decode(
             q.data_ptr(), _cabi.dtype_code(q),
             kp.data_ptr(), ks.data_ptr(), kz.data_ptr(),
@@ -127,7 +128,4 @@ def fused_decode_attention(
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
             B, HQ, HKV, S, D, nbits, gs, float(sm_scale), num_splits, split_size, nslots,
             _cabi.ptr(seq_lens), flags, stream))
-        if acc is not None and not _partials_only:
-            _cabi.check(lib.tkv_combine(acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(),
-                                        out.data_ptr(), None, None, B, HQ, nslots, D, stream))
     return out
