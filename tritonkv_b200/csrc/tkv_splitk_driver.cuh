@@ -49,7 +49,7 @@ struct SplitSched {
 };
 
 inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits, int split_size,
-                             bool ragged, int wave, int kTok) {
+                             bool ragged, int wave, int kTok, int warps) {
   SplitSched s{};
   s.NS = num_splits;
   s.HKVc = HKV * hchunks;
@@ -92,9 +92,12 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
     // the device is used and tile counts differ by at most one.
     if (units * 2 <= wave) {
       const int cpu = (int)(wave / units);
-      const int SEGu = s.TUf < cpu ? s.TUf : cpu;
+      // no more CTAs per unit than give every warp of a CTA a tile: spreading a short
+      // history thinner only adds partials for the combine to read
+      const int by_warps = (s.TUf + warps - 1) / warps;
+      const int SEGu = by_warps < cpu ? by_warps : cpu;
       const int TCu = (s.TUf + SEGu - 1) / SEGu;
-      if (TCu <= s.TC + 1) {
+      if (TCu <= s.TC + 1 || TCu <= warps) {
         s.persistent = 2;
         s.TC = TCu;
         s.SEG = SEGu;
@@ -710,7 +713,8 @@ struct SplitLaunch {
     int w = 0;
     int rc = wave(&w);
     if (rc != TKV_OK) return rc;
-    *sc = make_sched(B, HKV, hchunks, S, num_splits, split_size, ragged, w, Policy::TOK);
+    *sc = make_sched(B, HKV, hchunks, S, num_splits, split_size, ragged, w, Policy::TOK,
+                     Policy::WARPS);
     return TKV_OK;
   }
   static int launch(const typename Policy::Maps& maps, const DecodeParams& p, const SplitSched& sc,
