@@ -183,7 +183,7 @@ int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed, void* scal
  * (step parity, rank) of every rank's buffer.  tkv_merge_wait, enqueued after it on the
  * same stream, reads the world blocks of this step -- polling each pair until it carries
  * the step -- merges them into out (rows, D) and bumps the step.  The wait is bounded
- * (about 0.2 s); on expiry the kernel records bit 1 of tkv_device_status and merges what
+ * (2^18 polls, a few tenths of a second); on expiry the kernel records bit 1 of tkv_device_status and merges what
  * it has.  Ranks must call the pair in lockstep, one pair per decode step. */
 int tkv_combine_push(const float* acc, const float* m, const float* l, int64_t rows, int NS, int D,
                      int64_t acc_row_stride, int64_t acc_slot_stride, int64_t ml_row_stride,
@@ -198,6 +198,9 @@ int tkv_merge_wait(float* out, int64_t rows, int D, void* const* peer_data, void
  * tkv_merge_wait gave up.  No reference counterpart: the Triton kernels have no waits of
  * their own. */
 int tkv_device_status(int* status);
+
+/* Reset the status word of the current device to 0 (synchronises with it). */
+int tkv_device_status_clear(void);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,7 @@ SIGNATURES = {
     "tkv_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, POINTER(c_int), POINTER(c_int)]),
     "tkv_device_status": (c_int, [POINTER(c_int)]),
+    "tkv_device_status_clear": (c_int, []),
     "tkv_quantize_append": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                     c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "tkv_combine_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int64,
@@ -208,8 +209,13 @@ def kernel_attrs(kernel_id: int, nbits: int, D: int, gs: int) -> dict:
             "ctas_per_sm": vals[3].value}
 
 
+def device_status_clear() -> None:
+    check(load().tkv_device_status_clear())
+
+
 def device_status() -> int:
-    """0 = ok; 1 = a bounded wait inside a decode kernel gave up (synchronises)."""
+    """0 = ok; bit 0 = a bounded wait inside a decode kernel gave up, bit 1 = a bounded wait
+    for a peer's data in the cross-GPU merge gave up (synchronises)."""
     v = c_int(0)
     check(load().tkv_device_status(ctypes.byref(v)))
     return v.value

@@ -19,6 +19,9 @@ int fp16_attrs(int D, int* regs, int* smem, int* local, int* ctas);
 int fused_device_status(int* status);
 int fp16_device_status(int* status);
 int exchange_device_status(int* status);
+int fused_device_status_clear();
+int fp16_device_status_clear();
+int exchange_device_status_clear();
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
                int num_splits, int split_size, bool ragged);
 int fp16_plan(int D, SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
@@ -114,4 +117,12 @@ extern "C" int tkv_device_status(int* status) {
   if (rc != TKV_OK) return rc;
   *status = a | b | (c << 1);
   return TKV_OK;
+}
+
+extern "C" int tkv_device_status_clear(void) {
+  int rc = fused_device_status_clear();
+  if (rc != TKV_OK) return rc;
+  rc = fp16_device_status_clear();
+  if (rc != TKV_OK) return rc;
+  return exchange_device_status_clear();
 }

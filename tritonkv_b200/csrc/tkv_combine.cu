@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(kCombineThreads)
     uint2 ml = lane < 2 ? ld_volatile_pair(pml) : make_uint2(0u, step);
     int polls = 0;
     while (x.y != step || ml.y != step) {
-      if (++polls > (1 << 21)) {  // ~0.2 s with the pause below: a peer is gone
+      if (++polls > (1 << 18)) {  // a few tenths of a second with the pause below: a peer is gone
         atomicExch(&g_exchange_status, 1);
         break;
       }
@@ -292,6 +292,12 @@ __global__ void __launch_bounds__(kCombineThreads)
       ex.state[0] = step;
     }
   }
+}
+
+int exchange_device_status_clear() {
+  const int zero = 0;
+  TKV_CUDA(cudaMemcpyToSymbol(g_exchange_status, &zero, sizeof(int)));
+  return TKV_OK;
 }
 
 int exchange_device_status(int* status) {

@@ -238,6 +238,12 @@ int fp16_attrs(int D, int* regs, int* smem, int* local, int* ctas) {
   return fp16_unsupported(D);
 }
 
+int fp16_device_status_clear() {
+  const int zero = 0;
+  TKV_CUDA(cudaMemcpyToSymbol(g_fp16_status, &zero, sizeof(int)));
+  return TKV_OK;
+}
+
 int fp16_device_status(int* status) {
   int v = 0;
   TKV_CUDA(cudaMemcpyFromSymbol(&v, g_fp16_status, sizeof(int)));

@@ -706,6 +706,12 @@ int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int*
   return fused_unsupported(nbits, D, gs);
 }
 
+int fused_device_status_clear() {
+  const int zero = 0;
+  TKV_CUDA(cudaMemcpyToSymbol(g_fused_status, &zero, sizeof(int)));
+  return TKV_OK;
+}
+
 int fused_device_status(int* status) {
   int v = 0;
   TKV_CUDA(cudaMemcpyFromSymbol(&v, g_fused_status, sizeof(int)));
