@@ -498,3 +498,35 @@ def test_scale_zero_rows_at_every_alignment(nbits, D, gs, S):
     if (HKV * S * D * nbits // 8) % 16 == 0:  # the packed codes themselves need 16-byte alignment
         got = fused_decode_attention(q[1:].contiguous(), cut(kq), cut(vq))
         assert_close(got, ref[1:], "offset view")
+
+
+# ------------------------------------------------------------------ graphed serving step
+def test_graphed_decode_step_equals_direct_calls_and_follows_the_cache():
+    """GraphedDecodeStep replays H2D(q) + decode + D2H(out) as one graph: same bits as the
+    direct call, and a cache that grows in place (append + seq_lens on the device) is seen
+    by later replays without re-capturing."""
+    from tritonkv_b200 import GraphedDecodeStep
+
+    torch.manual_seed(11)
+    B, HQ, HKV, D, cap, nbits, gs = 2, 8, 2, 128, 300, 4, 32
+    k = torch.randn(B, HKV, cap, D, device=DEV, dtype=torch.float16)
+    v = torch.randn(B, HKV, cap, D, device=DEV, dtype=torch.float16)
+    kq = Q.empty_cache(B, HKV, cap, D, nbits, gs, DEV)
+    vq = Q.empty_cache(B, HKV, cap, D, nbits, gs, DEV)
+    n0 = 200
+    Q.append_kv(kq, vq, k[:, :, :n0], v[:, :, :n0], 0)
+    lens = torch.full((B,), n0, dtype=torch.int32, device=DEV)
+    step = GraphedDecodeStep(kq, vq, HQ, seq_lens=lens)
+    for t in range(n0, n0 + 40):
+        q = torch.randn(B, HQ, D, dtype=torch.float16)
+        step.run(q)
+        got = step.result().clone()
+        ref = fused_decode_attention(q.to(DEV), kq, vq, seq_lens=lens)
+        assert torch.equal(got, ref.cpu()), t
+        # the loop's write side: one more token, lengths bumped on the device
+        Q.append_kv(kq, vq, k[:, :, t:t + 1], v[:, :, t:t + 1], lens)
+        lens += 1
+    dense = Q.quantize_kv(k[:, :, :n0 + 40].contiguous(), v[:, :, :n0 + 40].contiguous(), nbits, gs)
+    q = torch.randn(B, HQ, D, dtype=torch.float16)
+    step.run(q)
+    assert_close(step.result(), oracle_attention(q.to(DEV), dense[0], dense[1]), "after 40 appends")

@@ -31,4 +31,6 @@ from .quantize import (  # noqa: F401
     roundtrip_error,
 )
 
+from .serving import GraphedDecodeStep  # noqa: F401,E402
+
 __version__ = "0.1.0"
