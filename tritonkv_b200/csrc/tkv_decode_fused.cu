@@ -130,7 +130,12 @@ __device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
 }
 
 
-template <int NBITS, int D_, int GS, int WARPS_ = 4, int STAGES_ = 3, int MIN_CTAS_ = 3>
+// A16: every scale/zero tile starts on a 16-byte boundary (the common case).  The other
+// instantiation serves caches whose rows start on smaller boundaries; keeping the two apart
+// keeps each kernel's instruction footprint small (a decode kernel usually starts with a
+// cold instruction cache, and the copy code is inlined at three places).
+template <int NBITS, int D_, int GS, bool A16 = true, int WARPS_ = 4, int STAGES_ = 3,
+          int MIN_CTAS_ = 3>
 struct FusedPolicy {
   using C = FusedCfg<NBITS, D_, GS>;
   static constexpr int D = D_;
@@ -203,28 +208,31 @@ struct FusedPolicy {
     // ~100+ cycles each, four of them per tile were a third of the loop time); every lane
     // then posts one arrival on the stage barrier that fires when its copies have landed.
     const uint32_t mst = st + 2 * C::CODE_BYTES;
-    if (NG == 1 && lane == 0)  // this tile's read-back shift (nonzero only on the path at the end)
-      asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(mst + C::SHIFT_WORD),
-                   "r"(p.meta_aligned == 0 ? (uint32_t)((p.meta_phase + row * 2) & 3) : 0u)
-                   : "memory");
-    if (NG > 1 && p.meta_aligned == 16 && nvalid == kTok) {
-      const int64_t off = (int64_t)row * (NG * 2);  // bytes
+    if constexpr (A16) {
+      if (NG == 1 && lane == 0)  // no read-back shift (see FusedCfg::META_STRIDE)
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(mst + C::SHIFT_WORD), "r"(0u) : "memory");
+      if (NG > 1 && nvalid == kTok) {
+        const int64_t off = (int64_t)row * (NG * 2);  // bytes
 #pragma unroll
-      for (int r = 0; r < ROUNDS; ++r) {
-        if (4 * CPA >= 32 || lane < 4 * CPA)
-          cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + off, 16);
+        for (int r = 0; r < ROUNDS; ++r) {
+          if (4 * CPA >= 32 || lane < 4 * CPA)
+            cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + off, 16);
+        }
+        cp_async_mbar_arrive_noinc(bar);
+      } else {
+        issue_meta<16>(p, row, nvalid, mst, bar, lane);
       }
-      cp_async_mbar_arrive_noinc(bar);
-    } else if (p.meta_aligned == 16) {
-      issue_meta<16>(p, row, nvalid, mst, bar, lane);
-    } else if (p.meta_aligned == 8) {
-      issue_meta<8>(p, row, nvalid, mst, bar, lane);
-    } else if (p.meta_aligned == 4) {
-      issue_meta<4>(p, row, nvalid, mst, bar, lane);
+    } else if constexpr (NG >= 4) {
+      issue_meta<8>(p, row, nvalid, mst, bar, lane);   // rows of 8 or 16 bytes
+    } else if constexpr (NG == 2) {
+      issue_meta<4>(p, row, nvalid, mst, bar, lane);   // rows of 4 bytes
     } else {
-      // one group per row and an odd history length: rows are aligned to 2 bytes only.
-      // Copy from the 4-byte boundary below and let the reader skip the first 2 bytes.
+      // one group per row: rows are aligned to 2 bytes only.  Copy from the 4-byte boundary
+      // below and let the reader skip the first `shift` bytes (0 when the tile is aligned).
       const int shift = (p.meta_phase + row * 2) & 3;  // 0 or 2
+      if (lane == 0)
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(mst + C::SHIFT_WORD), "r"((uint32_t)shift)
+                     : "memory");
       constexpr int N = C::META_BYTES / 4 + 1;  // 4-byte copies per array
       const int vbytes = nvalid * NG * 2 + shift;
       const int64_t off = (int64_t)row * (NG * 2) - shift;
@@ -238,6 +246,7 @@ struct FusedPolicy {
       }
       cp_async_mbar_arrive_noinc(bar);
     }
+    (void)st_ptr;
   }
 
   // Scale/zero of a tile in CS-byte copies: rows that only start on 8- or 4-byte boundaries
@@ -639,12 +648,19 @@ struct FusedPolicy {
 };
 
 // ------------------------------------------------------------------ host side
-#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)           \
-  if (nbits == NB && D == DD && gs == GG) {            \
-    using L = SplitLaunch<FusedPolicy<NB, DD, GG>>;    \
-    using C = FusedCfg<NB, DD, GG>;                    \
-    (void)sizeof(C);                                   \
-    return EXPR;                                       \
+#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)                  \
+  if (nbits == NB && D == DD && gs == GG) {                   \
+    using C = FusedCfg<NB, DD, GG>;                           \
+    (void)sizeof(C);                                          \
+    if (aligned16_rows) {                                     \
+      using P = FusedPolicy<NB, DD, GG, true>;                \
+      using L = SplitLaunch<P>;                               \
+      return EXPR;                                            \
+    } else {                                                  \
+      using P = FusedPolicy<NB, DD, GG, false>;               \
+      using L = SplitLaunch<P>;                               \
+      return EXPR;                                            \
+    }                                                         \
   }
 
 #define TKV_FUSED_ALL(EXPR)             \
@@ -670,9 +686,9 @@ static int fused_unsupported(int nbits, int D, int gs) {
   return TKV_ERR_UNSUPPORTED;
 }
 
-template <class L, class C>
+template <class L, class P, class C>
 static int fused_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStream_t stream) {
-  typename FusedPolicy<C::NBITS_, C::D_, C::GS_>::Maps maps;
+  typename P::Maps maps;
   const int64_t rows = (int64_t)p.B * p.HKV * p.S;
   int rc;
   if (p.wide) {
@@ -691,17 +707,20 @@ static int fused_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStr
 
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
                int num_splits, int split_size, bool ragged) {
+  constexpr bool aligned16_rows = true;  // both instantiations have the same resources
   TKV_FUSED_ALL(L::plan(sc, B, HKV, hchunks, S, num_splits, split_size, ragged))
   return fused_unsupported(nbits, D, gs);
 }
 
 static int fused_launch(int nbits, int D, int gs, const DecodeParams& p, const SplitSched& sc,
                         cudaStream_t stream) {
-  TKV_FUSED_ALL((fused_launch_one<L, C>(p, sc, stream)))
+  const bool aligned16_rows = p.meta_aligned == 16;
+  TKV_FUSED_ALL((fused_launch_one<L, P, C>(p, sc, stream)))
   return fused_unsupported(nbits, D, gs);
 }
 
 int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int* ctas) {
+  constexpr bool aligned16_rows = true;
   TKV_FUSED_ALL(L::attrs(regs, smem, local, ctas))
   return fused_unsupported(nbits, D, gs);
 }

@@ -203,7 +203,11 @@ struct IssueCursor {
   int g_end;      // end of the cursor's segment
 };
 
-template <class Policy>
+// MODE: 1 = balanced ranges over the dense tile sequence, 3 = the same over a ragged batch,
+// 2 = one segment per CTA (unit-aligned plans and the static plan).  A compile-time mode
+// keeps the single-segment kernel -- the latency-critical one, small batches -- free of the
+// segment look-ups, which are inlined at seven places in the others.
+template <class Policy, int MODE>
 __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     splitk_kernel(const __grid_constant__ typename Policy::Maps maps, const DecodeParams p,
                   const SplitSched sc) {
@@ -271,16 +275,24 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   int g0, g1;
   int TC = sc.TC;  // tiles per CTA (computed here for ragged batches)
   Segment seg;
+  constexpr bool kMulti = (MODE & 1) != 0;  // a CTA may serve several segments
   auto seg_at = [&](int g, int g_hi) {
-    return sc.persistent == 3 ? ragged_segment_at<kTok>(p, sc, s_pref, TC, g, g_hi, cta)
-                              : segment_at<kTok>(p, sc, g, g_hi, cta);
+    if constexpr (MODE == 3) {
+      return ragged_segment_at<kTok>(p, sc, s_pref, TC, g, g_hi, cta);
+    } else if constexpr (MODE == 1) {
+      return segment_at<kTok>(p, sc, g, g_hi, cta);
+    } else {
+      (void)g;
+      (void)g_hi;
+      return Segment{};
+    }
   };
-  if (sc.persistent == 1) {
+  if constexpr (MODE == 1) {
     g0 = min(cta * sc.TC, sc.T);
     g1 = min(g0 + sc.TC, sc.T);
     if (g0 >= g1) return;
     seg = segment_at<kTok>(p, sc, g0, g1, cta);
-  } else if (sc.persistent == 3) {
+  } else if constexpr (MODE == 3) {
     // balanced ranges over a ragged batch: every CTA builds the tile prefix of the
     // sequences (warp 0, 32 at a time), then cuts the global tile sequence evenly
     pdl_wait();
@@ -330,7 +342,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     g1 = min(g0 + TC, T);
     if (g0 >= g1) return;
     seg = seg_at(g0, g1);
-  } else if (sc.persistent == 2) {
+  } else if (sc.persistent == 2) {  // MODE 2 from here on
     // unit-aligned: CTA j of the unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG) of the unit
     const int u = cta / sc.SEG, j = cta - u * sc.SEG;
     const int bh = u / sc.NS;
@@ -401,10 +413,12 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   cursor_enter(cur, seg, g0);
   auto cursor_skip_empty = [&]() {
     // move to the next segment in which this warp has a tile (persistent mode only)
-    while (cur.cnt == 0 && (sc.persistent & 1) && cur.g_end < g1) {
-      const int g = cur.g_end;
-      const Segment s = seg_at(g, g1);
-      cursor_enter(cur, s, g);
+    if constexpr (kMulti) {
+      while (cur.cnt == 0 && cur.g_end < g1) {
+        const int g = cur.g_end;
+        const Segment s = seg_at(g, g1);
+        cursor_enter(cur, s, g);
+      }
     }
   };
   cursor_skip_empty();
@@ -436,11 +450,13 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // The query rows go first: behind the first tiles of every warp of the grid they would
   // queue for microseconds, ahead of them they arrive while the tiles are being issued.
   prefetch_q(0, seg.b, seg.hkv, seg.hc);
-#pragma unroll
+#pragma unroll 1  // one copy of the issue code here: a cold instruction cache pays per byte
   for (int s = 0; s < STAGES - 1; ++s) issue_next();
-  if ((sc.persistent & 1) && seg.g_end < g1) {
-    const Segment s1 = seg_at(seg.g_end, g1);
-    prefetch_q(1, s1.b, s1.hkv, s1.hc);
+  if constexpr (kMulti) {
+    if (seg.g_end < g1) {
+      const Segment s1 = seg_at(seg.g_end, g1);
+      prefetch_q(1, s1.b, s1.hkv, s1.hc);
+    }
   }
   int seg_k = 0;  // index of the current segment within this CTA
 
@@ -570,7 +586,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
         }
       }
     }
-    if (seg.fill_from >= 0) {
+    if (kMulti && seg.fill_from >= 0) {
       // this CTA finished the unit: mark the unit's unused partial slots empty
       const int nfill = seg.fill_to - seg.fill_from;
       for (int idx = threadIdx.x; idx < kHeadsPerCta * nfill; idx += WARPS * 32) {
@@ -586,15 +602,18 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     __syncthreads();
     need_proxy_fence = true;
 
-    if (!(sc.persistent & 1)) break;
-    g = seg.g_end;
-    if (g >= g1 || timed_out) break;
-    seg = seg_at(g, g1);
-    if (seg.g_end < g1) {  // the query slot just released takes the segment after the next
-      const Segment s2 = seg_at(seg.g_end, g1);
-      prefetch_q(seg_k & 1, s2.b, s2.hkv, s2.hc);
+    if constexpr (!kMulti) {
+      break;
+    } else {
+      g = seg.g_end;
+      if (g >= g1 || timed_out) break;
+      seg = seg_at(g, g1);
+      if (seg.g_end < g1) {  // the query slot just released takes the segment after the next
+        const Segment s2 = seg_at(seg.g_end, g1);
+        prefetch_q(seg_k & 1, s2.b, s2.hkv, s2.hc);
+      }
+      ++seg_k;
     }
-    ++seg_k;
   }
   if (timed_out && lane == 0) Policy::report_timeout();
 }
@@ -677,13 +696,17 @@ struct SplitLaunch {
            1024;                                    // slack for the 1024-byte alignment of the ring
   }
   static constexpr int kPrefixBytes = (kMaxRaggedB + 1) * 4 + 32;  // ragged batches: tile prefix
-  static const void* fn() { return reinterpret_cast<const void*>(&splitk_kernel<Policy>); }
+  template <int MODE>
+  static const void* fn_mode() { return reinterpret_cast<const void*>(&splitk_kernel<Policy, MODE>); }
+  static const void* fn() { return fn_mode<1>(); }  // same launch bounds and shared memory in all modes
   static int prepare() {
     static bool done[64] = {};
     int dev = 0;
     TKV_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && done[dev]) return TKV_OK;
-    TKV_CUDA(cudaFuncSetAttribute(fn(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TKV_CUDA(cudaFuncSetAttribute(fn_mode<1>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    TKV_CUDA(cudaFuncSetAttribute(fn_mode<2>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    TKV_CUDA(cudaFuncSetAttribute(fn_mode<3>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   smem_bytes() + kPrefixBytes));
     if (dev < 64) done[dev] = true;
     return TKV_OK;
@@ -728,14 +751,19 @@ struct SplitLaunch {
     // microseconds and all of them must be resident together, and measured under graph
     // replay a dependent launch placed one CTA per still-resident combine CTA late (by
     // 10-30 us at batch 16-32), which the static tile ranges cannot absorb.
+    const dim3 grid(sc.grid), block(Policy::WARPS * 32);
     if (sc.persistent == 2) {
-      TKV_CUDA(launch_pdl(splitk_kernel<Policy>, dim3(sc.grid), dim3(Policy::WARPS * 32),
-                          (size_t)smem_bytes(), stream, maps, p, sc));
-    } else {
-      const int smem = smem_bytes() + (sc.persistent == 3 ? kPrefixBytes : 0);
-      splitk_kernel<Policy><<<sc.grid, Policy::WARPS * 32, smem, stream>>>(maps, p, sc);
-      TKV_CUDA(cudaGetLastError());
+      TKV_CUDA(launch_pdl(splitk_kernel<Policy, 2>, grid, block, (size_t)smem_bytes(), stream, maps, p, sc));
+      return TKV_OK;
     }
+    if (sc.persistent == 1) {
+      splitk_kernel<Policy, 1><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
+    } else if (sc.persistent == 3) {
+      splitk_kernel<Policy, 3><<<grid, block, smem_bytes() + kPrefixBytes, stream>>>(maps, p, sc);
+    } else {
+      splitk_kernel<Policy, 2><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
+    }
+    TKV_CUDA(cudaGetLastError());
     return TKV_OK;
   }
   static int attrs(int* regs, int* smem, int* local, int* ctas) {
