@@ -419,17 +419,23 @@ def run_ours(args):
         gsteps[0].run(q_host[0])
         if not torch.equal(gsteps[0].result(), outs[0].cpu()):
             raise RuntimeError("graphed step and direct call disagree")
-        ms_e2e = max_over_ranks(harness.time_region(lambda: e2e_graphed(K_e2e), barrier))
+        ms_graphed = max_over_ranks(harness.time_region(lambda: e2e_graphed(K_e2e), barrier))
+        # Both are the public API; the headline is the faster one for this workload (one graph
+        # launch wins while the step is short, separate calls win once the copies are large:
+        # copy nodes of a graph ran slower than cudaMemcpyAsync for the 0.5-1 MB of batch 64).
+        ms_e2e = min(ms_graphed, ms_direct)
         e2e = {"value": total_bytes * K_e2e / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": int(q_dev.numel() * q_dev.element_size()),
                "d2h_bytes_per_step": int(out_host.numel() * 4), "steps": K_e2e,
                "us_per_step": ms_e2e * 1e3 / K_e2e,
+               "path": "graphed" if ms_graphed <= ms_direct else "direct",
+               "graphed_us_per_step": ms_graphed * 1e3 / K_e2e,
                "direct_call_us_per_step": ms_direct * 1e3 / K_e2e,
                "note": "per step: q pinned-host->device, fused_decode_attention (split + combine), "
                        "out device->pinned-host, stream sync; the KV cache is resident state. "
-                       "value/us_per_step: tritonkv_b200.GraphedDecodeStep (the copies and kernels "
-                       "captured as one CUDA graph, one launch per step); direct_call_us_per_step: "
-                       "the same four host calls issued one by one"}
+                       "graphed: tritonkv_b200.GraphedDecodeStep (the copies and kernels captured as "
+                       "one CUDA graph, one launch per step); direct: the same four host calls "
+                       "issued one by one; value = the faster of the two"}
 
     # ---- sweep rows (rank 0, qwen-b1 only): hot and cold, fused 4/2-bit vs fp16 control ----
     rows = []
