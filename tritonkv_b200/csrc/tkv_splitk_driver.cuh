@@ -225,7 +225,9 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   __shared__ float s_l[WARPS][kHeadsPerCta];
   __shared__ int s_slot[WARPS];
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle tells the compiler that the warp index is warp-uniform, so the ring, cursor and
+  // barrier arithmetic that hangs off it can go to the uniform datapath
+  const int warp = __shfl_sync(kFullMask, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
   // The whole grid is resident at once, so the combine kernel that follows may be
   // scheduled right away; it waits for this grid's completion before it reads anything.
