@@ -51,10 +51,10 @@ WORKLOADS = {
 # ncu capture summarised under profiles/ (None until a capture for that cell exists).
 NCU_TRAFFIC_BYTES = {
     # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.03 MB read + 0 written
-    "qwen-b1/4b/ctx65536": 21_033_472,
-    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.09 MB read + 2.7 MB written) at batch 16,
+    "qwen-b1/4b/ctx65536": 21_028_608,
+    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.08 MB read + 2.8 MB written) at batch 16,
     # scaled x4 to batch 64 (traffic is proportional to the cache bytes; L2 hit rate 1.3 %)
-    "llama8b-b64/4b/ctx4096": 4 * (84_085_760 + 2_696_320),
+    "llama8b-b64/4b/ctx4096": 4 * (84_083_328 + 2_799_616),
 }
 
 
