@@ -256,8 +256,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait: gives up after `limit` polls and reports false; never spins forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   int limit = 1 << 22) {
+  // all lanes of the warp wait on the same barrier: the vote makes the loop warp-uniform
   for (int i = 0; i < limit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+    if (__all_sync(kFullMask, mbar_try_wait(bar, parity))) return true;
   return false;
 }
 
