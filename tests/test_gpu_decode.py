@@ -530,3 +530,38 @@ def test_graphed_decode_step_equals_direct_calls_and_follows_the_cache():
     q = torch.randn(B, HQ, D, dtype=torch.float16)
     step.run(q)
     assert_close(step.result(), oracle_attention(q.to(DEV), dense[0], dense[1]), "after 40 appends")
+
+
+def test_combine_flag_equals_two_calls_through_the_c_abi():
+    """TKV_FLAG_COMBINE (split kernel + combine enqueued by one call) gives the bits of
+    tkv_fused_decode followed by tkv_combine."""
+    from tritonkv_b200 import _cabi
+    from tritonkv_b200.kernels._launch import split_geometry
+
+    B, HQ, HKV, D, S, nbits, gs = 2, 8, 2, 128, 3000, 4, 32
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=31)
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    lib = _cabi.load()
+    _, ns, ss = split_geometry(S, 64, None, B, HKV, None)
+    nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S, ns, ss, False)
+    assert nslots > 1
+    stream = _cabi.stream_ptr(q.device)
+    outs = []
+    for flags in (0, _cabi.FLAG_COMBINE):
+        acc = torch.empty(B, HQ, nslots, D, device=DEV)
+        m = torch.empty(B, HQ, nslots, device=DEV)
+        l = torch.empty(B, HQ, nslots, device=DEV)
+        out = torch.full((B, HQ, D), float("nan"), device=DEV)
+        _cabi.check(lib.tkv_fused_decode(
+            q.data_ptr(), _cabi.dtype_code(q), kq.packed.data_ptr(), kq.scale.data_ptr(),
+            kq.zero.data_ptr(), vq.packed.data_ptr(), vq.scale.data_ptr(), vq.zero.data_ptr(),
+            acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(), B, HQ, HKV, S, D, nbits, gs,
+            1.0 / D ** 0.5, ns, ss, nslots, None, flags, stream))
+        if flags == 0:
+            assert torch.isnan(out).all()  # partials only: out untouched
+            _cabi.check(lib.tkv_combine(acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(),
+                                        None, None, B, HQ, nslots, D, stream))
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    assert_close(outs[1], oracle_attention(q, kq, vq), "combine flag")
