@@ -197,14 +197,20 @@ __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
   asm volatile("ld.volatile.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// A {value, step} pair moves as ONE 64-bit access: the memory model gives single-copy
+// atomicity to an aligned 8-byte scalar access, not to the two halves of a vector access,
+// and the protocol needs the step never to be seen without its value.
 __device__ __forceinline__ uint2 ld_volatile_pair(const uint2* p) {
+  uint64_t w;
+  asm volatile("ld.volatile.global.u64 %0, [%1];\n" : "=l"(w) : "l"(p) : "memory");
   uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  asm("mov.b64 {%0,%1}, %2;\n" : "=r"(v.x), "=r"(v.y) : "l"(w));
   return v;
 }
 __device__ __forceinline__ void st_volatile_pair(uint2* p, float x, uint32_t step) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};\n" ::"l"(p), "r"(__float_as_uint(x)), "r"(step)
-               : "memory");
+  uint64_t w;
+  asm("mov.b64 %0, {%1,%2};\n" : "=l"(w) : "r"(__float_as_uint(x)), "r"(step));
+  asm volatile("st.volatile.global.u64 [%0], %1;\n" ::"l"(p), "l"(w) : "memory");
 }
 
 __global__ void __launch_bounds__(kCombineThreads)

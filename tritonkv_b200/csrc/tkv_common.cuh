@@ -60,13 +60,6 @@ __device__ __forceinline__ void cp_async_n(uint32_t dst, const void* src, int sr
                  : "memory");
   }
 }
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;\n" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -187,10 +180,6 @@ __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
   __half2 h = __halves2half2(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
 
 // Load element `i` of a query row of any supported dtype, rounded to f16 exactly
 // as the reference's `.to(tl.float16)` does, returned as float.
@@ -229,11 +218,6 @@ __device__ __forceinline__ void fence_proxy_async() {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
                : "memory");
-}
-// Plain arrival (count 1) with release semantics: this thread's earlier shared-memory
-// writes are visible to whoever observes the phase complete.
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 // Arrival (count 1, pre-accounted in the barrier's init count) that fires when all
 // cp.async copies this thread issued before it have landed.
@@ -275,15 +259,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
       "l"(tensor_map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-// 1-D bulk copy global -> shared; src, dst 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
-                                             uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
-          "r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
 

@@ -86,22 +86,6 @@ struct MetaRow {
   uint32_t w[(NG + 1) / 2];  // NG halves
 };
 template <int NG>
-__device__ __forceinline__ MetaRow<NG> load_meta_row(const __half* p) {
-  MetaRow<NG> r;
-  if constexpr (NG == 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
-  } else if constexpr (NG == 4) {
-    const uint2 v = *reinterpret_cast<const uint2*>(p);
-    r.w[0] = v.x; r.w[1] = v.y;
-  } else if constexpr (NG == 2) {
-    r.w[0] = *reinterpret_cast<const uint32_t*>(p);
-  } else {
-    r.w[0] = *reinterpret_cast<const uint16_t*>(p);
-  }
-  return r;
-}
-template <int NG>
 __device__ __forceinline__ MetaRow<NG> lds_meta_row(uint32_t addr) {
   MetaRow<NG> r;
   if constexpr (NG == 8) {

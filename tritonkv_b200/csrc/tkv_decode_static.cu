@@ -18,6 +18,9 @@ static __device__ __align__(256) float g_decode_scratch[kScratchFloats];
 
 // In host code the array's name is only a handle for the runtime, not a device address,
 // so the address is asked for once per device (with that device current) and cached.
+// Concurrent first calls may both do the look-up and store the same value.  The cache
+// does not survive cudaDeviceReset: a process that resets a device must not call this
+// entry point on that device afterwards.
 constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {};
 
@@ -53,7 +56,12 @@ extern "C" int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t
   int rc = tkv_decode_plan(TKV_KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S, 1, split_size, 0,
                            &nslots, nullptr);
   if (rc != TKV_OK) return rc;
-  if (nslots == 1)  // nothing to merge: no scratch involved at all
+  // The one-time look-up of the scratch address happens on the first call on a device,
+  // whatever the plan of that call, so that a warm-up call always completes the set-up.
+  float* base = nullptr;
+  rc = scratch_for_current_device(&base);
+  if (rc != TKV_OK) return rc;
+  if (nslots == 1)  // nothing to merge: the scratch is not touched
     return tkv_fused_decode(q, q_dtype, k_packed, k_scale, k_zero, v_packed, v_scale, v_zero,
                             nullptr, nullptr, nullptr, out, B, HQ, HKV, S, D, nbits, gs, sm_scale,
                             1, split_size, 1, nullptr, 0, stream);
@@ -63,9 +71,6 @@ extern "C" int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t
               "fused_decode_static: B*HQ*nslots*(D+2) = %zu floats of partials exceed the built-in "
               "scratch of %zu floats (8 MiB); use tkv_fused_decode with caller-owned buffers",
               need, kScratchFloats);
-  float* base = nullptr;
-  rc = scratch_for_current_device(&base);
-  if (rc != TKV_OK) return rc;
   float* acc = base;
   float* m = base + rows * D;
   float* l = m + rows;

@@ -196,12 +196,15 @@ using namespace tkv;
 extern "C" int tkv_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t rows, int D, int nbits,
                               void* stream) {
   TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
-  TKV_REQUIRE(codes && packed && rows >= 0 && D > 0, TKV_ERR_INVALID, "pack_codes: bad arguments");
+  TKV_REQUIRE(rows >= 0 && D > 0, TKV_ERR_INVALID, "pack_codes: bad sizes rows=%lld D=%d",
+              (long long)rows, D);
   const int P = 8 / nbits;
   TKV_REQUIRE(D % P == 0, TKV_ERR_INVALID, "head_dim %d must be divisible by %d for %d-bit packing",
               D, P, nbits);
   const int64_t n = rows * (D / P);
-  if (n == 0) return TKV_OK;
+  if (n == 0) return TKV_OK;  // an empty tensor has no storage: nothing to check, nothing to do
+  TKV_REQUIRE(codes && packed, TKV_ERR_INVALID, "pack_codes: null pointer");
+  TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "pack_codes: tensor too large");
   const int blocks = (int)((n + 255) / 256);
   if (nbits == 4)
     pack_codes_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(codes, packed, n, D);
@@ -214,11 +217,14 @@ extern "C" int tkv_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t row
 extern "C" int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t rows, int D,
                                 int nbits, void* stream) {
   TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
-  TKV_REQUIRE(codes && packed && rows >= 0 && D > 0, TKV_ERR_INVALID, "unpack_codes: bad arguments");
+  TKV_REQUIRE(rows >= 0 && D > 0, TKV_ERR_INVALID, "unpack_codes: bad sizes rows=%lld D=%d",
+              (long long)rows, D);
   const int P = 8 / nbits;
   TKV_REQUIRE(D % P == 0, TKV_ERR_INVALID, "head_dim %d must be divisible by %d", D, P);
   const int64_t n = rows * D;
   if (n == 0) return TKV_OK;
+  TKV_REQUIRE(codes && packed, TKV_ERR_INVALID, "unpack_codes: null pointer");
+  TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "unpack_codes: tensor too large");
   const int blocks = (int)((n + 255) / 256);
   if (nbits == 4)
     unpack_codes_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(packed, codes, n, D);
@@ -249,10 +255,11 @@ int launch_quantize(const void* x, uint8_t* packed, void* scale, void* zero, int
 extern "C" int tkv_quantize_pack(const void* x, int in_dtype, uint8_t* packed, void* scale,
                                  void* zero, int64_t rows, int D, int nbits, int gs, void* stream) {
   TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
-  TKV_REQUIRE(x && packed && scale && zero && rows >= 0, TKV_ERR_INVALID,
-              "quantize_pack: bad arguments");
+  TKV_REQUIRE(rows >= 0, TKV_ERR_INVALID, "quantize_pack: rows=%lld", (long long)rows);
   TKV_REQUIRE(gs > 0 && D > 0 && D % gs == 0, TKV_ERR_INVALID,
               "group_size %d must divide head_dim %d", gs, D);
+  if (rows == 0) return TKV_OK;  // an empty tensor has no storage: nothing to check, nothing to do
+  TKV_REQUIRE(x && packed && scale && zero, TKV_ERR_INVALID, "quantize_pack: null pointer");
   // One thread owns 8 elements; a row (<= 256 elements) and a group must map to
   // whole, aligned lane ranges of one warp.
   TKV_REQUIRE(pow2(D) && D >= 16 && D <= 256 && pow2(gs) && gs >= 8, TKV_ERR_UNSUPPORTED,
@@ -262,7 +269,6 @@ extern "C" int tkv_quantize_pack(const void* x, int in_dtype, uint8_t* packed, v
               "quantize_pack: packed row of %d bytes is not a multiple of 8", D * nbits / 8);
   TKV_REQUIRE(aligned16(x) && ((uintptr_t)packed & 7u) == 0, TKV_ERR_ALIGN,
               "quantize_pack: x must be 16-byte and packed 8-byte aligned");
-  if (rows == 0) return TKV_OK;
   cudaStream_t s = (cudaStream_t)stream;
   switch (in_dtype) {
     case TKV_DTYPE_F16: return launch_quantize<__half>(x, packed, scale, zero, rows, D, nbits, gs, s);
@@ -289,7 +295,8 @@ extern "C" int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed,
                                    void* zero, int B, int HKV, int T_new, int64_t S_cap, int D,
                                    int nbits, int gs, const int32_t* positions, int pos0,
                                    void* stream) {
-  TKV_REQUIRE(x && packed && scale && zero, TKV_ERR_INVALID, "quantize_append: null pointer");
+  TKV_REQUIRE((x || T_new == 0) && packed && scale && zero, TKV_ERR_INVALID,
+              "quantize_append: null pointer");
   TKV_REQUIRE(B > 0 && HKV > 0 && T_new >= 0 && S_cap > 0, TKV_ERR_INVALID,
               "quantize_append: bad sizes B=%d HKV=%d T_new=%d S_cap=%lld", B, HKV, T_new,
               (long long)S_cap);
@@ -334,11 +341,11 @@ int launch_dequant(const uint8_t* packed, const void* scale, const void* zero, v
 extern "C" int tkv_dequantize(const uint8_t* packed, const void* scale, const void* zero, void* out,
                               int out_dtype, int64_t rows, int D, int nbits, int gs, void* stream) {
   TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
-  TKV_REQUIRE(packed && scale && zero && out && rows >= 0, TKV_ERR_INVALID,
-              "dequantize: bad arguments");
+  TKV_REQUIRE(rows >= 0, TKV_ERR_INVALID, "dequantize: rows=%lld", (long long)rows);
   TKV_REQUIRE(gs > 0 && D > 0 && D % gs == 0 && D % (8 / nbits) == 0, TKV_ERR_INVALID,
               "dequantize: group_size %d must divide head_dim %d", gs, D);
   if (rows == 0) return TKV_OK;
+  TKV_REQUIRE(packed && scale && zero && out, TKV_ERR_INVALID, "dequantize: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   switch (out_dtype) {
     case TKV_DTYPE_F16: return launch_dequant<__half>(packed, scale, zero, out, rows, D, nbits, gs, s);

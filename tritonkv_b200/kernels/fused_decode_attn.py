@@ -17,7 +17,7 @@ import math
 import torch
 
 from .. import _cabi
-from ..quantize import QuantizedTensor
+from ..quantize import QuantizedTensor, check_cache_tensors
 from ._launch import (check_out, check_seq_lens, combine_splits, get_workspace, pick_num_splits,
                       q_for_kernel, split_geometry)
 
@@ -95,6 +95,8 @@ def fused_decode_attention(
     _cabi.require_cuda(kq.packed, "kq.packed")
 
     device = q.device
+    check_cache_tensors(kq, "kq", device)
+    check_cache_tensors(vq, "vq", device)
     sm_scale = 1.0 / math.sqrt(D) if sm_scale is None else sm_scale
     nbits, gs = kq.nbits, kq.group_size
 

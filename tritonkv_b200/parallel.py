@@ -121,24 +121,54 @@ class PeerExchange:
     arrived, then the cross-rank merge).  Ranks call the pair in lockstep, once per decode step."""
 
     def __init__(self, B: int, HQ: int, D: int, device, group=None):
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm_mem
+        import os
 
+        import torch.distributed as dist
+
+        # The kernels use plain peer stores only.  Without this switch the rendezvous also
+        # binds the buffer to an NVLink multicast object on NVLS-capable machines, which
+        # nothing here uses and which turns a rank that exits early into link faults on its
+        # peers.  It has to be set before the first symmetric-memory call of the process.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("the peer exchange serves at most 8 ranks")
         self.rows, self.D, self.wire = B * HQ, D, wire_floats(B, HQ, D)
         state_off, total = exchange_layout(self.world, self.wire)
-        self.buf = symm_mem.empty(total // 4, dtype=torch.float32, device=device)
-        self.buf.zero_()
-        torch.cuda.synchronize(device)
+        # Allocation can fail on one rank only (no symmetric-memory support, no memory); the
+        # rendezvous is a collective, so the ranks first agree that everyone has a buffer.
+        err = None
+        self.buf = self.handle = None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.buf = symm_mem.empty(total // 4, dtype=torch.float32, device=device)
+            self.buf.zero_()
+            torch.cuda.synchronize(device)
+        except Exception as exc:
+            err = exc
+        flag = torch.tensor([0 if err is not None else 1], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if not bool(flag.item()):
+            self.buf = None
+            raise RuntimeError(f"symmetric memory is not available on every rank (this rank: {err!r})")
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         dist.barrier(group)  # every rank has zeroed its buffer before anyone pushes
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         table = ctypes.c_void_p * self.world
         self.data_ptrs = table(*ptrs)
         self.state_ptr = ptrs[self.rank] + state_off
+
+    def close(self) -> None:
+        """Drop the mapping of the peers' buffers and this rank's own buffer.  Call on every
+        rank, with no step in flight, before the process group is destroyed."""
+        if self.buf is not None:
+            torch.cuda.synchronize(self.buf.device)
+        self.data_ptrs = None
+        self.state_ptr = 0
+        self.handle = None
+        self.buf = None
 
     def push(self, acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor) -> None:
         """``acc (B, HQ, NS, D)``, ``m, l (B, HQ, NS)``: this rank's split partials."""
@@ -188,19 +218,22 @@ class HistorySplitDecoder:
         self.peer = None
         self._empty: dict = {}
         if exchange != "nccl" and self.world <= 8:
-            err = None
+            # PeerExchange agrees across the ranks before its collective set-up, so either
+            # every rank gets one or every rank raises.
             try:
                 self.peer = PeerExchange(B, HQ, D, device, group)
-            except Exception as exc:  # symmetric memory unavailable on this system
-                err = exc
-            # every rank must take the same path
-            flag = torch.tensor([0 if self.peer is None else 1], device=device)
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-            if not bool(flag.item()):
-                self.peer = None
+            except RuntimeError:
                 if exchange == "peer":
-                    raise RuntimeError(f"peer exchange could not be set up on every rank: {err!r}")
+                    raise
+                self.peer = None
         self.exchange = "peer" if self.peer is not None else "nccl"
+
+    def close(self) -> None:
+        """Release the peer mappings (see :meth:`PeerExchange.close`); the decoder cannot
+        step afterwards."""
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
 
     def local_partial(self, q, kq, vq, sm_scale=None):
         """Rank-local unnormalised partial written into the wire buffer."""

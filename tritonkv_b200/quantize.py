@@ -107,6 +107,23 @@ class QuantizedTensor:
         )
 
 
+def check_cache_tensors(qt: "QuantizedTensor", what: str, device) -> None:
+    """The kernels read ``packed`` as bytes and ``scale``/``zero`` as fp16 on one device:
+    anything else would be reinterpreted silently, so it is refused here.  (The reference's
+    Triton loads accept any float dtype for the metadata; its quantiser only ever produces
+    fp16, quantize.py:222-229.)"""
+    if qt.packed.dtype != torch.uint8:
+        raise TypeError(f"{what}.packed must be uint8, got {qt.packed.dtype}")
+    for name in ("scale", "zero"):
+        t = getattr(qt, name)
+        if t.dtype != torch.float16:
+            raise TypeError(f"{what}.{name} must be float16, got {t.dtype}; convert with .half()")
+    for name in ("packed", "scale", "zero"):
+        t = getattr(qt, name)
+        if t.device != device:
+            raise ValueError(f"{what}.{name} is on {t.device}, expected {device}")
+
+
 def _rows(t: torch.Tensor) -> int:
     n = 1
     for s in t.shape[:-1]:
@@ -189,6 +206,7 @@ def dequantize_groupwise(qt: QuantizedTensor, dtype: torch.dtype = torch.float32
     lib = _cabi.load()
     if dtype not in (torch.float16, torch.bfloat16, torch.float32):
         raise TypeError(f"unsupported dtype {dtype}; expected float16, bfloat16 or float32")
+    check_cache_tensors(qt, "qt", qt.packed.device)
     packed, scale, zero = qt.packed.contiguous(), qt.scale.contiguous(), qt.zero.contiguous()
     out = torch.empty((*packed.shape[:-1], qt.head_dim), dtype=dtype, device=packed.device)
     code = {torch.float16: _cabi.DTYPE_F16, torch.bfloat16: _cabi.DTYPE_BF16,
