@@ -192,6 +192,17 @@ int tkv_combine_push(const float* acc, const float* m, const float* l, int64_t r
 int tkv_merge_wait(float* out, int64_t rows, int D, void* const* peer_data, void* state, int world,
                    int rank, int wire_floats, void* stream);
 
+/* tkv_combine_push and tkv_merge_wait as ONE kernel (no reference counterpart): the CTA that
+ * merges this rank's partials of a (row, 32-dim slice) stores the result to every rank and
+ * then waits -- with the same bounded wait -- for the same slice of every rank, merges and
+ * writes out (rows, D).  One kernel boundary less on the latency chain of a history-split
+ * step; same buffers, state words and lockstep rule as the pair above, with which it must
+ * not be mixed within one step. */
+int tkv_combine_exchange(const float* acc, const float* m, const float* l, float* out, int64_t rows,
+                         int NS, int D, int64_t acc_row_stride, int64_t acc_slot_stride,
+                         int64_t ml_row_stride, int64_t ml_slot_stride, void* const* peer_data,
+                         void* state, int world, int rank, int wire_floats, void* stream);
+
 /* Device-side status word of the current device (synchronises with it): 0 = ok,
  * bit 0 = a bounded wait on a copy barrier inside a decode kernel gave up (the kernel then
  * returned early and its output is invalid), bit 1 = a bounded wait for a peer's data in

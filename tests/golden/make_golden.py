@@ -88,6 +88,31 @@ def main(ref_root: str) -> None:
             out[f"zero_{key}"] = qt.zero.numpy()
     np.savez_compressed(os.path.join(HERE, "quantize.npz"), **out)
 
+    # ---- 2b. quantiser edges the reference's own tests do not pin --------
+    # group ranges that underflow fp16 (scale rounds to a subnormal or to 0, codes
+    # collapse to {0, qmax}), a constant group, +inf / -inf / NaN inside a group
+    out = {}
+    g = torch.Generator().manual_seed(99)
+    xe = torch.zeros(6, 128)
+    xe[0] = torch.randn(128, generator=g) * 1e-7
+    xe[1] = 1.0 + torch.randn(128, generator=g) * 1e-8
+    xe[2] = torch.randn(128, generator=g)
+    xe[2, 5] = float("inf")
+    xe[3] = torch.randn(128, generator=g)
+    xe[3, 40] = float("-inf")
+    xe[4] = torch.randn(128, generator=g)
+    xe[4, 70] = float("nan")
+    xe[5] = torch.randn(128, generator=g) * 1e-5
+    out["x_edges"] = xe.numpy()
+    for nbits in (2, 4):
+        for gs in (32, 128):
+            qt = rq.quantize_groupwise(xe, nbits, gs)
+            key = f"edges_n{nbits}_g{gs}"
+            out[f"packed_{key}"] = qt.packed.numpy()
+            out[f"scale_{key}"] = qt.scale.numpy()
+            out[f"zero_{key}"] = qt.zero.numpy()
+    np.savez_compressed(os.path.join(HERE, "quantize_edges.npz"), **out)
+
     # ---- 3. attention ground truth ----------------------------------------
     out = {}
     att_cases = [

@@ -16,7 +16,7 @@ from tritonkv_b200.kernels import (combine_splits, fp16_decode_attention, fused_
                                    triton_available)
 from tritonkv_b200.workloads import make_random_kv, ragged_seq_lens
 
-from util import ATOL, RTOL, assert_close, oracle_attention, to_oracle
+from util import ATOL, RTOL, assert_close, c_oracle_attention, oracle_attention, to_oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -475,6 +475,50 @@ def test_llama70b_long_context_full_size():
     ref = c_oracle.decode_step(q.float().cpu().numpy(), h(kq.packed), h(kq.scale), h(kq.zero),
                                h(vq.packed), h(vq.scale), h(vq.zero), 2, 32)
     assert_close(got, ref, "llama-70b ctx 131072 2-bit")
+
+
+@pytest.mark.parametrize("nbits", [4, 2])
+def test_llama8b_batch64_full_size_against_oracle(nbits):
+    """Llama-3-8B-shaped decode at its full size (batch 64, HQ 32 / HKV 8, ctx 4096): the
+    balanced dense schedule whose CTAs straddle unit boundaries and mark unused slots empty.
+    Eight sampled sequences -- first, last and six between -- against the C twin of the
+    oracle; every other sequence through the split-count invariance below."""
+    B, HQ, HKV, S, D = 64, 32, 8, 4096, 128
+    g = torch.Generator(device=DEV).manual_seed(21 + nbits)
+    q = torch.randn(B, HQ, D, generator=g, device=DEV).half()
+    k = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    v = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    kq, vq = Q.quantize_kv(k, v, nbits, 32)
+    del k, v
+    got = fused_decode_attention(q, kq, vq)
+    rows = [0, 9, 18, 27, 36, 45, 54, 63]
+    ref = c_oracle_attention(q, kq, vq, rows=rows)
+    assert_close(got[rows], ref, f"batch 64 x ctx 4096, {nbits}-bit, sampled sequences")
+    # a different cut of the same work (explicit splits: static units) agrees everywhere
+    other = fused_decode_attention(q, kq, vq, num_splits=3)
+    assert (got - other).abs().max().item() < 2e-3
+
+
+@pytest.mark.parametrize("D,HQ,HKV,nbits,gs", [(128, 32, 8, 4, 32), (128, 8, 1, 2, 64),
+                                               (64, 32, 8, 2, 32), (64, 8, 1, 4, 64)])
+def test_ragged_sweep_full_lengths_against_oracle(D, HQ, HKV, nbits, gs):
+    """One cell per (head_dim, heads) of the ragged batched sweep at its real lengths (batch
+    16, lengths uniform in [1024, 32768] from the seed, 1 % of the K entries x20): the
+    longest, the shortest and two more sequences against the C twin of the oracle."""
+    B, S_max = 16, 32768
+    lens = ragged_seq_lens(B, 1024, S_max, seed=D + HQ)
+    S = int(lens.max())
+    g = torch.Generator(device=DEV).manual_seed(17)  # drawn on the device: 0.5 G values at HKV 8
+    q = torch.randn(B, HQ, D, generator=g, device=DEV).half()
+    k = torch.randn(B, HKV, S, D, generator=g, device=DEV)
+    k = torch.where(torch.rand(B, HKV, S, D, generator=g, device=DEV) < 0.01, k * 20.0, k).half()
+    v = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    kq, vq = Q.quantize_kv(k, v, nbits, gs)
+    del k, v
+    got = fused_decode_attention(q, kq, vq, seq_lens=lens.to(DEV))
+    rows = sorted({int(lens.argmax()), int(lens.argmin()), 3, 11})
+    ref = c_oracle_attention(q, kq, vq, seq_lens=lens, rows=rows)
+    assert_close(got[rows], ref, f"ragged full lengths D={D} {HQ}/{HKV} {nbits}b gs={gs}")
 
 
 # ------------------------------------------------------------------ metadata alignment

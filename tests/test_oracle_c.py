@@ -42,6 +42,19 @@ def test_quantize_pack_dequantize_bit_exact(C, nbits, D, gs):
     assert np.array_equal(deq.view(np.uint32), O.dequantize_groupwise(ref).view(np.uint32))
 
 
+@pytest.mark.parametrize("nbits", [2, 4])
+@pytest.mark.parametrize("gs", [32, 128])
+def test_quantize_edges_match_the_reference_fixture(C, golden_dir, nbits, gs):
+    from test_oracle_golden import f16_equal
+
+    g = np.load(os.path.join(golden_dir, "quantize_edges.npz"))
+    packed, scale, zero = c_oracle.quantize_groupwise(g["x_edges"], nbits, gs)
+    key = f"edges_n{nbits}_g{gs}"
+    assert f16_equal(scale, g[f"scale_{key}"])
+    assert f16_equal(zero, g[f"zero_{key}"])
+    assert np.array_equal(packed, g[f"packed_{key}"])
+
+
 @pytest.mark.parametrize("name", ["cfg1", "qwen_s17_2b", "mha_d64", "llama_b2_d64_g64",
                                   "gqa8_g128_2b", "gqa4_g16"])
 def test_decode_step_matches_golden(C, golden_dir, name):

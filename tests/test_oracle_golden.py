@@ -26,6 +26,29 @@ def test_pack_known_answers(golden_dir):
     assert np.array_equal(O.pack_codes(g["pack2_known_codes"], 2), g["pack2_known_packed"])
 
 
+def f16_equal(a, b):
+    """Bit patterns of two fp16 arrays agree; NaNs agree with NaNs whatever their payload."""
+    a, b = np.asarray(a).view(np.float16), np.asarray(b).view(np.float16)
+    nan = np.isnan(a)
+    return bool(np.array_equal(nan, np.isnan(b)) and
+                np.array_equal(a.view(np.uint16)[~nan], b.view(np.uint16)[~nan]))
+
+
+@pytest.mark.parametrize("nbits", [2, 4])
+@pytest.mark.parametrize("gs", [32, 128])
+def test_quantize_edges_bit_exact(golden_dir, nbits, gs):
+    """Edges the reference's own tests leave open, pinned on what its quantiser returns:
+    group ranges that underflow fp16 (scale becomes a subnormal or 0 and the codes collapse
+    to {0, qmax}), a constant group, and +inf / -inf / NaN inside a group (scale inf or 1,
+    zero -inf or NaN, codes 0)."""
+    g = _load(golden_dir, "quantize_edges.npz")
+    qt = O.quantize_groupwise(g["x_edges"], nbits, gs)
+    key = f"edges_n{nbits}_g{gs}"
+    assert f16_equal(qt.scale, g[f"scale_{key}"])
+    assert f16_equal(qt.zero, g[f"zero_{key}"])
+    assert np.array_equal(qt.packed, g[f"packed_{key}"])
+
+
 @pytest.mark.parametrize("nbits", [2, 4])
 @pytest.mark.parametrize("D", [64, 128])
 def test_pack_unpack_bit_exact(golden_dir, nbits, D):

@@ -30,3 +30,17 @@ def assert_close(got: torch.Tensor, ref: np.ndarray, what=""):
     assert rep["cosine"] >= KERNEL_COSINE_MIN, f"{what}: {rep}"
     assert rep["rel_l2"] <= KERNEL_REL_L2_MAX, f"{what}: {rep}"
     return rep
+
+
+def c_oracle_attention(q, kq, vq, seq_lens=None, rows=None) -> np.ndarray:
+    """The oracle's C twin (same arithmetic, OpenMP) for cases too large for numpy; ``rows``
+    selects the sequences to compute (all if None)."""
+    from oracle import c_oracle
+
+    idx = torch.arange(q.shape[0]) if rows is None else torch.as_tensor(list(rows))
+    it = idx.to(q.device)
+    h = lambda t: t.index_select(0, it).cpu().numpy()
+    hm = lambda t: h(t).view(np.uint16)
+    sl = None if seq_lens is None else seq_lens.cpu().index_select(0, idx).numpy()
+    return c_oracle.decode_step(h(q.float()), h(kq.packed), hm(kq.scale), hm(kq.zero), h(vq.packed),
+                                hm(vq.scale), hm(vq.zero), kq.nbits, kq.group_size, seq_lens=sl)

@@ -66,6 +66,9 @@ SIGNATURES = {
                                  c_void_p]),
     "tkv_merge_wait": (c_int, [c_void_p, c_int64, c_int, POINTER(c_void_p), c_void_p, c_int, c_int,
                                c_int, c_void_p]),
+    "tkv_combine_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                     c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p), c_void_p,
+                                     c_int, c_int, c_int, c_void_p]),
     "tkv_fused_decode_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_float, c_void_p]),

@@ -213,45 +213,15 @@ __device__ __forceinline__ void st_volatile_pair(uint2* p, float x, uint32_t ste
   asm volatile("st.volatile.global.u64 [%0], %1;\n" ::"l"(p), "l"(w) : "memory");
 }
 
-__global__ void __launch_bounds__(kCombineThreads)
-    combine_push_kernel(const float* __restrict__ acc, const float* __restrict__ m,
-                        const float* __restrict__ l, int NS, int D, int64_t a_row, int64_t a_slot,
-                        int64_t ml_row, int64_t ml_slot, const Exchange ex) {
-  const int tid = threadIdx.x;
-  const int row = blockIdx.x;
-  const int d0 = blockIdx.y * kCombineSlice;
-  pdl_launch_dependents();
-  pdl_wait();
-  const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
-  if (tid < 8) {
-    const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the wait-merge kernel only
-    const int64_t blk = (int64_t)((step & 1) * ex.world + ex.rank) * ex.wire;
-    const int64_t e = (int64_t)row * D + d0 + tid * 4;
-    for (int j = 0; j < ex.world; ++j) {
-      uint2* dst = ex.data[j] + blk;
-      st_volatile_pair(dst + e, c.r.x, step);
-      st_volatile_pair(dst + e + 1, c.r.y, step);
-      st_volatile_pair(dst + e + 2, c.r.z, step);
-      st_volatile_pair(dst + e + 3, c.r.w, step);
-      if (tid == 0 && blockIdx.y == 0) {
-        st_volatile_pair(dst + (int64_t)ex.rows * D + row, c.M, step);
-        st_volatile_pair(dst + (int64_t)ex.rows * D + ex.rows + row, c.L, step);
-      }
-    }
-  }
-}
-
-// One CTA per (row, 32-dim slice): warp j reads rank j's block, lane = dim inside the slice.
-__global__ void __launch_bounds__(kCombineThreads)
-    merge_wait_kernel(float* __restrict__ out, int D, const Exchange ex) {
+// Cross-rank half of the exchange for one (row, 32-dim slice): warp j reads rank j's block of
+// this step, lane = dim inside the slice, polling (bounded) until each pair carries the
+// step; then the log-sum-exp merge, the store of the normalised output, and the ticket that
+// lets the last CTA of the grid bump the step.
+__device__ __forceinline__ void wait_merge_store(float* __restrict__ out, int D, const Exchange& ex,
+                                                 uint32_t step, int row, int d0) {
   __shared__ float sh_x[kMaxPeers][kCombineSlice];
   __shared__ float sh_ml[kMaxPeers][2];
   const int tid = threadIdx.x, j = tid >> 5, lane = tid & 31;
-  const int row = blockIdx.x;
-  const int d0 = blockIdx.y * kCombineSlice;
-  pdl_launch_dependents();
-  pdl_wait();  // orders this kernel after the previous wait-merge (the step counter) and the push
-  const uint32_t step = ld_volatile_u32(ex.state) + 1;
   if (j < ex.world) {
     const uint2* src = ex.data[ex.rank] + (int64_t)((step & 1) * ex.world + j) * ex.wire;
     const uint2* px = src + (int64_t)row * D + d0 + lane;
@@ -288,7 +258,7 @@ __global__ void __launch_bounds__(kCombineThreads)
     out[(int64_t)row * D + d0 + tid] = L > 0.f ? a / L : 0.f;
   }
   // the last CTA to get here bumps the step (local memory only; nothing waits on it
-  // inside this grid, and the next push follows this grid in the stream)
+  // inside this grid, and the next exchange follows this grid in the stream)
   if (tid == 0) {
     const uint32_t total = gridDim.x * gridDim.y;
     const uint32_t ticket = atomicAdd(ex.state + 1, 1u);
@@ -298,6 +268,70 @@ __global__ void __launch_bounds__(kCombineThreads)
       ex.state[0] = step;
     }
   }
+}
+
+// Stores the merged (row, slice) of this rank, tagged with the step, into block
+// (step parity, own rank) of every rank's receive buffer.  Threads 0..7 hold the result.
+__device__ __forceinline__ void push_to_peers(const CombineResult& c, const Exchange& ex, uint32_t step,
+                                              int D, int row, int d0, bool first_slice) {
+  const int tid = threadIdx.x;
+  if (tid < 8) {
+    const int64_t blk = (int64_t)((step & 1) * ex.world + ex.rank) * ex.wire;
+    const int64_t e = (int64_t)row * D + d0 + tid * 4;
+    for (int j = 0; j < ex.world; ++j) {
+      uint2* dst = ex.data[j] + blk;
+      st_volatile_pair(dst + e, c.r.x, step);
+      st_volatile_pair(dst + e + 1, c.r.y, step);
+      st_volatile_pair(dst + e + 2, c.r.z, step);
+      st_volatile_pair(dst + e + 3, c.r.w, step);
+      if (tid == 0 && first_slice) {
+        st_volatile_pair(dst + (int64_t)ex.rows * D + row, c.M, step);
+        st_volatile_pair(dst + (int64_t)ex.rows * D + ex.rows + row, c.L, step);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kCombineThreads)
+    combine_push_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                        const float* __restrict__ l, int NS, int D, int64_t a_row, int64_t a_slot,
+                        int64_t ml_row, int64_t ml_slot, const Exchange ex) {
+  const int row = blockIdx.x;
+  const int d0 = blockIdx.y * kCombineSlice;
+  pdl_launch_dependents();
+  pdl_wait();
+  const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
+  const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the wait-merge kernel only
+  push_to_peers(c, ex, step, D, row, d0, blockIdx.y == 0);
+}
+
+// One CTA per (row, 32-dim slice).
+__global__ void __launch_bounds__(kCombineThreads)
+    merge_wait_kernel(float* __restrict__ out, int D, const Exchange ex) {
+  pdl_launch_dependents();
+  pdl_wait();  // orders this kernel after the previous wait-merge (the step counter) and the push
+  const uint32_t step = ld_volatile_u32(ex.state) + 1;
+  wait_merge_store(out, D, ex, step, blockIdx.x, blockIdx.y * kCombineSlice);
+}
+
+// The whole exchange in one kernel: the CTA of a (row, slice) merges this rank's split
+// partials, stores the result to every rank, then waits for the same (row, slice) of every
+// rank and finishes.  Pushes never wait on anything and every CTA pushes before it waits,
+// so no wait can depend on a CTA that has not been scheduled: the grid (rows x D/32 CTAs of
+// 256 threads) is far below one wave, and a CTA only ever waits for REMOTE stores.
+__global__ void __launch_bounds__(kCombineThreads)
+    combine_exchange_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                            const float* __restrict__ l, float* __restrict__ out, int NS, int D,
+                            int64_t a_row, int64_t a_slot, int64_t ml_row, int64_t ml_slot,
+                            const Exchange ex) {
+  const int row = blockIdx.x;
+  const int d0 = blockIdx.y * kCombineSlice;
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the last CTA of the previous exchange
+  const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
+  push_to_peers(c, ex, step, D, row, d0, blockIdx.y == 0);
+  wait_merge_store(out, D, ex, step, row, d0);
 }
 
 int exchange_device_status_clear() {
@@ -476,6 +510,26 @@ extern "C" int tkv_combine_push(const float* acc, const float* m, const float* l
   TKV_CUDA(launch_pdl(tkv::combine_push_kernel, grid, dim3(kCombineThreads), 0, (cudaStream_t)stream,
                       acc, m, l, NS, D, acc_row_stride, acc_slot_stride, ml_row_stride,
                       ml_slot_stride, ex));
+  return TKV_OK;
+}
+
+extern "C" int tkv_combine_exchange(const float* acc, const float* m, const float* l, float* out,
+                                    int64_t rows, int NS, int D, int64_t acc_row_stride,
+                                    int64_t acc_slot_stride, int64_t ml_row_stride,
+                                    int64_t ml_slot_stride, void* const* peer_data, void* state,
+                                    int world, int rank, int wire_floats, void* stream) {
+  using namespace tkv;
+  TKV_REQUIRE(acc && m && l && out, TKV_ERR_INVALID, "combine_exchange: null pointer");
+  TKV_REQUIRE(NS > 0, TKV_ERR_INVALID, "combine_exchange: NS=%d", NS);
+  TKV_REQUIRE(aligned16(acc) && acc_row_stride % 4 == 0 && acc_slot_stride % 4 == 0, TKV_ERR_ALIGN,
+              "combine_exchange: acc must be 16-byte aligned, strides multiples of 4");
+  Exchange ex{};
+  int rc = fill_exchange(ex, peer_data, state, world, rank, rows, D, wire_floats);
+  if (rc != TKV_OK) return rc;
+  dim3 grid((unsigned)rows, D / kCombineSlice);
+  TKV_CUDA(launch_pdl(tkv::combine_exchange_kernel, grid, dim3(kCombineThreads), 0,
+                      (cudaStream_t)stream, acc, m, l, out, NS, D, acc_row_stride, acc_slot_stride,
+                      ml_row_stride, ml_slot_stride, ex));
   return TKV_OK;
 }
 

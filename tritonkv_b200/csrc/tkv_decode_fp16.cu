@@ -20,6 +20,7 @@ struct Fp16Policy {
   static constexpr int WARPS = 4;
   static constexpr int STAGES = (D_ >= 128) ? 3 : 4;
   static constexpr int MIN_CTAS = 2;
+  static constexpr bool PIPELINED = true;
   static constexpr int BAR_COUNT = 32;  // one arrival per lane
   static constexpr int ROW = 2 * D;            // bytes per token row
   static constexpr int NH = ROW / 128;         // 128-byte column halves per row

@@ -47,10 +47,11 @@
 
 namespace tkv {
 
-constexpr int kTok = 32;  // tokens per tile / stage
-
-template <int NBITS, int D, int GS>
+template <int NBITS, int D, int GS, int TOK_ = 32>
 struct FusedCfg {
+  static constexpr int kTok = TOK_;     // tokens per tile / stage
+  static constexpr int MT = kTok / 16;  // 16-token MMA blocks per tile
+  static_assert(kTok == 32 || kTok == 64, "a tile is 32 or 64 tokens");
   static constexpr int NBITS_ = NBITS, D_ = D, GS_ = GS;
   static constexpr int P = 8 / NBITS;          // codes per byte = bit slices
   static constexpr int DP = D / P;             // packed bytes per token
@@ -118,12 +119,14 @@ __device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
 // instantiation serves caches whose rows start on smaller boundaries; keeping the two apart
 // keeps each kernel's instruction footprint small (a decode kernel usually starts with a
 // cold instruction cache, and the copy code is inlined at three places).
-template <int NBITS, int D_, int GS, bool A16 = true, int WARPS_ = 4, int STAGES_ = 3,
-          int MIN_CTAS_ = 3>
+template <int NBITS, int D_, int GS, bool A16 = true, int TOK_ = 32, int WARPS_ = 4, int STAGES_ = 3,
+          int MIN_CTAS_ = 3, bool PIPELINED_ = true>
 struct FusedPolicy {
-  using C = FusedCfg<NBITS, D_, GS>;
+  using C = FusedCfg<NBITS, D_, GS, TOK_>;
   static constexpr int D = D_;
+  static constexpr int kTok = C::kTok, MT = C::MT;
   static constexpr int TOK = kTok;
+  static constexpr bool PIPELINED = PIPELINED_;
   static constexpr int WARPS = WARPS_;
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MIN_CTAS_;
@@ -140,7 +143,7 @@ struct FusedPolicy {
     uint32_t qf[NCH][2];  // B operand of the score MMA; bit slice p is pre-scaled by 2^(-NBITS p)
     uint32_t qz0, qz1;    // B operand of the K zero-point MMA: f16 hi / lo parts of
                           // qk_scale * (sum of q over a group), groups 2t and 2t+1
-    uint32_t off[2][C::NPAIR];  // this lane's ldmatrix byte offsets inside a code tile
+    uint32_t off[MT][C::NPAIR];  // this lane's ldmatrix byte offsets inside a code tile
     uint32_t o_row;   // byte offset of token g's row inside a scale array
     uint32_t o_kz;    // byte offset of this lane's K zero-point word (token g)
     uint32_t o_vz;    // byte offset of this lane's first V zero-point (token 2t, group g mod NG)
@@ -264,7 +267,7 @@ struct FusedPolicy {
     const int lm_r = (lane & 7) + ((lane >> 3) & 1) * 8;
     const int lm_b = (NBLK >= 2) ? (lane >> 4) : 0;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int pr = 0; pr < C::NPAIR; ++pr) {
         const int n = 16 * mt + lm_r, blk = 2 * pr + lm_b;
@@ -382,10 +385,10 @@ struct FusedPolicy {
   }
 
   struct Scores {
-    float s[2][4];  // [16-token half][(token g, head 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)]
+    float s[MT][4];  // [16-token block][(token g, head 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)]
   };
 
-  // Scores of one 32-token tile in stage `st` (scaled by qk_scale, tokens past the unit
+  // Scores of one tile in stage `st` (scaled by qk_scale, tokens past the unit
   // end set to -inf); `left` = tokens from the tile start to the unit end.
   __device__ static __forceinline__ void scores(Scores& out, const Query& qq, uint32_t st,
                                                 const uint8_t*, int left, float qk_scale,
@@ -399,9 +402,9 @@ struct FusedPolicy {
     const float qk24 = qk_scale * 16777216.f;  // the code fields carry 2^-24
     constexpr int HALF = 16 * NG * 2;           // bytes of 16 token rows in a metadata array
 
-    float (&sc)[2][4] = out.s;
+    float (&sc)[MT][4] = out.s;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int mt = 0; mt < MT; ++mt) {
       float c[NACC][4];
       bool started[NACC];  // resolved at compile time: the loops below are fully unrolled
 #pragma unroll
@@ -480,7 +483,7 @@ struct FusedPolicy {
     }
     if (left < kTok) {
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int mt = 0; mt < MT; ++mt) {
         if (mt * 16 + g >= left) sc[mt][0] = sc[mt][1] = -INFINITY;
         if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
       }
@@ -496,13 +499,18 @@ struct FusedPolicy {
     const uint32_t vs_a = ms + 2 * C::META_STRIDE + qq.o_row;
     const uint32_t vz_a = ms + 3 * C::META_STRIDE + qq.o_vz;
     constexpr int HALF = 16 * NG * 2;
-    float (&sc)[2][4] = in.s;
+    float (&sc)[MT][4] = in.s;
     // ---- online softmax with a lazily raised reference exponent ----
     {
       // this lane's maxima for heads 2t / 2t+1; the cross-lane maximum is only needed
       // when some lane exceeds the reference (rare) and in finalize
-      float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
-      float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+      float mx0 = fmaxf(sc[0][0], sc[0][2]);
+      float mx1 = fmaxf(sc[0][1], sc[0][3]);
+#pragma unroll
+      for (int mt = 1; mt < MT; ++mt) {
+        mx0 = fmaxf(mx0, fmaxf(sc[mt][0], sc[mt][2]));
+        mx1 = fmaxf(mx1, fmaxf(sc[mt][1], sc[mt][3]));
+      }
       ac.m_true0 = fmaxf(ac.m_true0, mx0);
       ac.m_true1 = fmaxf(ac.m_true1, mx1);
       if (__any_sync(kFullMask, (mx0 > ac.m_ref0) || (mx1 > ac.m_ref1))) {
@@ -530,7 +538,7 @@ struct FusedPolicy {
         ac.zacc[3] *= alpha1;
       }
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
+      for (int mt = 0; mt < MT; ++mt) {
         sc[mt][0] = ex2(sc[mt][0] - ac.m_ref0);
         sc[mt][1] = ex2(sc[mt][1] - ac.m_ref1);
         sc[mt][2] = ex2(sc[mt][2] - ac.m_ref0);
@@ -540,7 +548,7 @@ struct FusedPolicy {
 
     // ---- output: O^T += V^T P^T ----
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
+    for (int mt = 0; mt < MT; ++mt) {
       const uint32_t ph_lo = pack_half2(sc[mt][0], sc[mt][1]);  // token g,   heads 2t, 2t+1
       const uint32_t ph_hi = pack_half2(sc[mt][2], sc[mt][3]);  // token g+8
       {
@@ -632,19 +640,35 @@ struct FusedPolicy {
 };
 
 // ------------------------------------------------------------------ host side
-#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)                  \
-  if (nbits == NB && D == DD && gs == GG) {                   \
-    using C = FusedCfg<NB, DD, GG>;                           \
-    (void)sizeof(C);                                          \
-    if (aligned16_rows) {                                     \
-      using P = FusedPolicy<NB, DD, GG, true>;                \
-      using L = SplitLaunch<P>;                               \
-      return EXPR;                                            \
-    } else {                                                  \
-      using P = FusedPolicy<NB, DD, GG, false>;               \
-      using L = SplitLaunch<P>;                               \
-      return EXPR;                                            \
-    }                                                         \
+// Two kernel families per (nbits, head_dim, group_size, row alignment):
+//  * batched -- 4 warps, ring of 3 stages, software-pipelined tile loop, 3 CTAs per SM: the
+//    balanced schedules (modes 1 and 3), where a CTA streams tens of tiles per warp;
+//  * long -- 8 warps, ring of 2 stages, one tile at a time, 2 CTAs per SM: few long units
+//    (mode 2: small batches, and the static one-CTA-per-unit plan).  The same 16 warps per SM
+//    in two thirds of the CTAs: a third fewer partial slots for the merge that follows and a
+//    third fewer query loads and epilogues, which is what a step of 2-3 tiles per warp is
+//    made of (measured: batch 1, ctx 65536, 4-bit step 12.4 -> 10.8 us).
+constexpr int kVariantBatched = 0, kVariantLong = 1;
+template <int NB, int DD, int GG, bool A16>
+using BatchedPolicy = FusedPolicy<NB, DD, GG, A16, 32, 4, 3, 3, true>;
+template <int NB, int DD, int GG, bool A16>
+using LongPolicy = FusedPolicy<NB, DD, GG, A16, 32, 8, 2, 2, false>;
+
+#define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)                        \
+  if (nbits == NB && D == DD && gs == GG) {                         \
+    if (aligned16_rows) {                                           \
+      using PB = BatchedPolicy<NB, DD, GG, true>;                   \
+      using PL = LongPolicy<NB, DD, GG, true>;                      \
+      using LB = SplitLaunch<PB, 0xA>;                              \
+      using LL = SplitLaunch<PL, 0x4>;                              \
+      return EXPR;                                                  \
+    } else {                                                        \
+      using PB = BatchedPolicy<NB, DD, GG, false>;                  \
+      using PL = LongPolicy<NB, DD, GG, false>;                     \
+      using LB = SplitLaunch<PB, 0xA>;                              \
+      using LL = SplitLaunch<PL, 0x4>;                              \
+      return EXPR;                                                  \
+    }                                                               \
   }
 
 #define TKV_FUSED_ALL(EXPR)             \
@@ -670,42 +694,61 @@ static int fused_unsupported(int nbits, int D, int gs) {
   return TKV_ERR_UNSUPPORTED;
 }
 
-template <class L, class P, class C>
+template <class L, class P>
 static int fused_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStream_t stream) {
+  using C = typename P::C;
   typename P::Maps maps;
   const int64_t rows = (int64_t)p.B * p.HKV * p.S;
   int rc;
   if (p.wide) {
-    // [bytes/128, 128] view, box = the 32 tokens' bytes as 128-byte rows, 128B swizzle
-    rc = make_row_map(&maps.k, p.kp, rows * C::DP / 128, 128, 128, kTok * C::DP / 128);
+    // [bytes/128, 128] view, box = a tile's bytes as 128-byte rows, 128B swizzle
+    rc = make_row_map(&maps.k, p.kp, rows * C::DP / 128, 128, 128, C::kTok * C::DP / 128);
     if (rc != TKV_OK) return rc;
-    rc = make_row_map(&maps.v, p.vp, rows * C::DP / 128, 128, 128, kTok * C::DP / 128);
+    rc = make_row_map(&maps.v, p.vp, rows * C::DP / 128, 128, 128, C::kTok * C::DP / 128);
   } else {
-    rc = make_row_map(&maps.k, p.kp, rows, C::DP, C::DP, kTok);
+    rc = make_row_map(&maps.k, p.kp, rows, C::DP, C::DP, C::kTok);
     if (rc != TKV_OK) return rc;
-    rc = make_row_map(&maps.v, p.vp, rows, C::DP, C::DP, kTok);
+    rc = make_row_map(&maps.v, p.vp, rows, C::DP, C::DP, C::kTok);
   }
   if (rc != TKV_OK) return rc;
   return L::launch(maps, p, sc, stream);
 }
 
+// The long family plans first: if its plan is a mode-2 one (unit-aligned, or static units for
+// ragged batches with explicit splits) it is taken, otherwise the batched family plans.
+template <class LB, class LL>
+static int fused_plan_both(SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
+                           int split_size, bool ragged) {
+  int rc = LL::plan(sc, B, HKV, hchunks, S, num_splits, split_size, ragged);
+  if (rc != TKV_OK) return rc;
+  if (sc->persistent == 2 || sc->persistent == 0) {
+    sc->variant = kVariantLong;
+    return TKV_OK;
+  }
+  rc = LB::plan(sc, B, HKV, hchunks, S, num_splits, split_size, ragged);
+  sc->variant = kVariantBatched;
+  return rc;
+}
+
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
                int num_splits, int split_size, bool ragged) {
   constexpr bool aligned16_rows = true;  // both instantiations have the same resources
-  TKV_FUSED_ALL(L::plan(sc, B, HKV, hchunks, S, num_splits, split_size, ragged))
+  TKV_FUSED_ALL((fused_plan_both<LB, LL>(sc, B, HKV, hchunks, S, num_splits, split_size, ragged)))
   return fused_unsupported(nbits, D, gs);
 }
 
 static int fused_launch(int nbits, int D, int gs, const DecodeParams& p, const SplitSched& sc,
                         cudaStream_t stream) {
   const bool aligned16_rows = p.meta_aligned == 16;
-  TKV_FUSED_ALL((fused_launch_one<L, P, C>(p, sc, stream)))
+  TKV_FUSED_ALL((sc.variant == kVariantLong ? fused_launch_one<LL, PL>(p, sc, stream)
+                                            : fused_launch_one<LB, PB>(p, sc, stream)))
   return fused_unsupported(nbits, D, gs);
 }
 
+// Resources of the batched family (the one that runs where bandwidth binds).
 int fused_attrs(int nbits, int D, int gs, int* regs, int* smem, int* local, int* ctas) {
   constexpr bool aligned16_rows = true;
-  TKV_FUSED_ALL(L::attrs(regs, smem, local, ctas))
+  TKV_FUSED_ALL(LB::attrs(regs, smem, local, ctas))
   return fused_unsupported(nbits, D, gs);
 }
 

@@ -75,16 +75,22 @@ __global__ void __launch_bounds__(256)
   float v[8];
   load8<T>(x + r * D + 8 * c, v);
   float mn = v[0], mx = v[0];
+  bool has_nan = v[0] != v[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) {
     mn = fminf(mn, v[i]);
     mx = fmaxf(mx, v[i]);
+    has_nan |= v[i] != v[i];
   }
   const int lanes_per_group = gs >> 3;
   for (int off = 1; off < lanes_per_group; off <<= 1) {
     mn = fminf(mn, __shfl_xor_sync(kFullMask, mn, off));
     mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, off));
+    has_nan |= __shfl_xor_sync(kFullMask, (int)has_nan, off) != 0;
   }
+  // torch's amin/amax propagate NaN where fminf/fmaxf drop it: a group that holds a NaN
+  // gets zero = NaN, scale = 1 and all codes 0, as the reference produces.
+  if (has_nan) mn = mx = __int_as_float(0x7fc00000);
   float sc = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
   sc = (sc > 0.f) ? sc : 1.f;
   const __half sc16 = __float2half_rn(sc);

@@ -15,7 +15,11 @@
 // Inside a CTA every warp is an independent stream with a private ring of STAGES
 // shared-memory stages and one mbarrier per stage.  Lane 0 issues the copies of a
 // tile (Policy::issue); the ring keeps running across segment boundaries, so the next
-// unit's first tiles are already in flight while a segment's epilogue runs.  Warps
+// unit's first tiles are already in flight while a segment's epilogue runs.  The tile
+// loop has two forms (Policy::PIPELINED): a software pipeline that holds two tiles per
+// warp (scores of tile i+1 beside the update of tile i; needs STAGES >= 3), and a
+// one-tile-at-a-time form whose body exists once per ring slot (STAGES >= 2), which
+// fits more warps per SM in the same shared memory.  Warps
 // only meet at a segment end: each writes its partial into its one free stage, the
 // CTA merges the warps' partials (log-sum-exp) and stores the segment's partial or,
 // when a unit has a single slot, the normalised output.
@@ -24,6 +28,8 @@
 #pragma once
 
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "tkv_split_common.cuh"
 
@@ -46,10 +52,13 @@ struct SplitSched {
   int nslots;      // NS * SEG
   int grid;        // CTAs
   int HKVc;        // HKV * head chunks
+  int variant;     // which kernel instantiation the plan was made for (set by the planner)
 };
 
+// `unit_aligned`: whether the plan may be the unit-aligned one (mode 2); a kernel family that
+// is only built for the balanced modes passes false.
 inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits, int split_size,
-                             bool ragged, int wave, int kTok, int warps) {
+                             bool ragged, int wave, int kTok, int warps, bool unit_aligned = true) {
   SplitSched s{};
   s.NS = num_splits;
   s.HKVc = HKV * hchunks;
@@ -90,7 +99,7 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
     // when it lengthens the longest CTA by at most one tile.
     // CTA j of a unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG): every resident slot of
     // the device is used and tile counts differ by at most one.
-    if (units * 2 <= wave) {
+    if (unit_aligned && units * 2 <= wave) {
       const int cpu = (int)(wave / units);
       // no more CTAs per unit than give every warp of a CTA a tile: spreading a short
       // history thinner only adds partials for the combine to read
@@ -215,7 +224,10 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   constexpr int kTok = Policy::TOK;
   constexpr int STAGE_BYTES = Policy::STAGE_BYTES;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte alignment");
-  static_assert(STAGES >= 3, "two tiles are resident at once (scores of i+1, update of i)");
+  static_assert(STAGES >= (Policy::PIPELINED ? 3 : 2),
+                "pipelined: two tiles resident and one in flight; else one resident, one in flight");
+  static_assert(Policy::PIPELINED || STAGES <= 3,
+                "the per-slot tile bodies are written for rings of 2 or 3 stages");
   static_assert(STAGE_BYTES >= kHeadsPerCta * D * 4, "a stage must hold one warp's partial");
 
   extern __shared__ uint8_t smem_raw[];
@@ -429,10 +441,9 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // per tile.
   int iss_slot = 0;  // slot the next issue fills
   bool need_proxy_fence = false;
-  auto issue_next = [&]() {
+  auto issue_at = [&](int slot) {
     if (cur.cnt == 0) return;
-    const int slot = iss_slot;
-    iss_slot = (iss_slot + 1 == STAGES) ? 0 : iss_slot + 1;
+    iss_slot = (slot + 1 == STAGES) ? 0 : slot + 1;
     if (need_proxy_fence) {  // a generic-proxy epilogue touched the ring since the last issue
       fence_proxy_async();
       need_proxy_fence = false;
@@ -444,6 +455,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     --cur.cnt;
     cursor_skip_empty();
   };
+  auto issue_next = [&]() { issue_at(iss_slot); };
   typename Policy::Query qs;
   Policy::lane_init(qs, p, lane);
   // Launched as a programmatic dependent: everything above ran while the previous kernel
@@ -453,7 +465,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // queue for microseconds, ahead of them they arrive while the tiles are being issued.
   prefetch_q(0, seg.b, seg.hkv, seg.hc);
 #pragma unroll 1  // one copy of the issue code here: a cold instruction cache pays per byte
-  for (int s = 0; s < STAGES - 1; ++s) issue_next();
+  for (int s = 0; s < (Policy::PIPELINED ? STAGES - 1 : STAGES); ++s) issue_next();
   if constexpr (kMulti) {
     if (seg.g_end < g1) {
       const Segment s1 = seg_at(seg.g_end, g1);
@@ -464,6 +476,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
 
   int c_slot = 0, c_phase = 0;  // slot and barrier phase of the next tile to consume
   bool timed_out = false;
+  bool deferred_issue = false;  // one-tile form: the refill of the stage that carries the partial
   typename Policy::Accum acc;
 
   for (int g = g0;;) {
@@ -477,48 +490,85 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     Policy::reset(acc);
     const int my_tiles = seg.ntiles > warp ? (seg.ntiles - warp + WARPS - 1) / WARPS : 0;
     int left = seg.hi - (seg.lo_tok + warp * kTok);
-    // Software pipeline: the scores of tile i+1 are computed in the same straight-line
-    // block as the softmax/output update of tile i, so the two independent dependency
-    // chains interleave in the instruction stream.
-    if (my_tiles > 0 && !timed_out) {
-      typename Policy::Scores sc_cur;
-      if (!mbar_wait_bounded(bar_u32 + 8 * c_slot, c_phase)) timed_out = true;
-      __syncwarp();
-      if (!timed_out)
-        Policy::scores(sc_cur, qs, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES, left,
-                       p.qk_scale, lane);
-      for (int i = 1; i < my_tiles && !timed_out; ++i) {
-        int n_slot = c_slot + 1, n_phase = c_phase;
-        if (n_slot == STAGES) {
-          n_slot = 0;
-          n_phase ^= 1;
+    if constexpr (Policy::PIPELINED) {
+      // Software pipeline: the scores of tile i+1 are computed in the same straight-line
+      // block as the softmax/output update of tile i, so the two independent dependency
+      // chains interleave in the instruction stream.
+      if (my_tiles > 0 && !timed_out) {
+        typename Policy::Scores sc_cur;
+        if (!mbar_wait_bounded(bar_u32 + 8 * c_slot, c_phase)) timed_out = true;
+        __syncwarp();
+        if (!timed_out)
+          Policy::scores(sc_cur, qs, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES, left,
+                         p.qk_scale, lane);
+        for (int i = 1; i < my_tiles && !timed_out; ++i) {
+          int n_slot = c_slot + 1, n_phase = c_phase;
+          if (n_slot == STAGES) {
+            n_slot = 0;
+            n_phase ^= 1;
+          }
+          if (!mbar_wait_bounded(bar_u32 + 8 * n_slot, n_phase)) {
+            timed_out = true;
+            break;
+          }
+          __syncwarp();
+          issue_next();  // refills the stage whose tile was finished in the previous iteration
+          typename Policy::Scores sc_next;
+          Policy::scores(sc_next, qs, ring_u32 + n_slot * STAGE_BYTES, ring + n_slot * STAGE_BYTES,
+                         left - WARPS * kTok, p.qk_scale, lane);
+          Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
+                         left, lane);
+          sc_cur = sc_next;
+          left -= WARPS * kTok;
+          c_slot = n_slot;
+          c_phase = n_phase;
         }
-        if (!mbar_wait_bounded(bar_u32 + 8 * n_slot, n_phase)) {
+        if (!timed_out) {
+          __syncwarp();
+          issue_next();
+          Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
+                         left, lane);
+          if (++c_slot == STAGES) {
+            c_slot = 0;
+            c_phase ^= 1;
+          }
+        }
+      }
+    } else {
+      // One tile at a time: scores then update on the same stage, which is refilled (STAGES
+      // tiles ahead) as soon as its tile is finished -- except after the segment's last tile:
+      // that stage carries the warp's partial through the epilogue and is refilled after it.
+      // The body exists once per ring slot, so every shared-memory address in it is a
+      // compile-time offset from the warp's ring.
+      auto tile = [&](auto slot_c, bool last) {
+        constexpr int SL = decltype(slot_c)::value;
+        if (!mbar_wait_bounded(bar_u32 + 8 * SL, c_phase)) {
           timed_out = true;
-          break;
+          return;
         }
         __syncwarp();
-        issue_next();  // refills the stage whose tile was finished in the previous iteration
-        typename Policy::Scores sc_next;
-        Policy::scores(sc_next, qs, ring_u32 + n_slot * STAGE_BYTES, ring + n_slot * STAGE_BYTES,
-                       left - WARPS * kTok, p.qk_scale, lane);
-        Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
-                       left, lane);
-        sc_cur = sc_next;
+        typename Policy::Scores sc_cur;
+        Policy::scores(sc_cur, qs, ring_u32 + SL * STAGE_BYTES, ring + SL * STAGE_BYTES, left,
+                       p.qk_scale, lane);
+        Policy::update(acc, qs, sc_cur, ring_u32 + SL * STAGE_BYTES, ring + SL * STAGE_BYTES, left,
+                       lane);
         left -= WARPS * kTok;
-        c_slot = n_slot;
-        c_phase = n_phase;
-      }
-      if (!timed_out) {
+        if constexpr (SL == STAGES - 1) c_phase ^= 1;
+        c_slot = (SL + 1 == STAGES) ? 0 : SL + 1;
         __syncwarp();
-        issue_next();
-        Policy::update(acc, qs, sc_cur, ring_u32 + c_slot * STAGE_BYTES, ring + c_slot * STAGE_BYTES,
-                       left, lane);
-        if (++c_slot == STAGES) {
-          c_slot = 0;
-          c_phase ^= 1;
+        if (!last) issue_at(SL);  // in ring order the next issue always refills the slot just consumed
+      };
+      for (int i = 0; i < my_tiles && !timed_out; ++i) {
+        const bool last = i + 1 == my_tiles;
+        if (c_slot == 0) {
+          tile(std::integral_constant<int, 0>{}, last);
+        } else if (STAGES == 2 || c_slot == 1) {
+          tile(std::integral_constant<int, 1>{}, last);
+        } else {
+          tile(std::integral_constant<int, STAGES - 1>{}, last);
         }
       }
+      deferred_issue = my_tiles > 0 && !timed_out;
     }
 
     // ---- segment epilogue: merge the warps, store the partial ----
@@ -544,13 +594,14 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     {
       constexpr int D4 = D / 4;
       constexpr int ITEMS = kHeadsPerCta * D4;
-      static_assert(ITEMS % (WARPS * 32) == 0, "merge items must tile the CTA");
+      constexpr int ROUNDS = (ITEMS + WARPS * 32 - 1) / (WARPS * 32);
       uint32_t voff[WARPS];
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) voff[w] = (uint32_t)((w * STAGES + s_slot[w]) * STAGE_BYTES);
 #pragma unroll
-      for (int it = 0; it < ITEMS / (WARPS * 32); ++it) {
+      for (int it = 0; it < ROUNDS; ++it) {
         const int idx = it * (WARPS * 32) + threadIdx.x;
+        if (ITEMS % (WARPS * 32) != 0 && idx >= ITEMS) break;
         const int h = idx / D4, d = (idx - h * D4) * 4;
         const int hg = seg.hc * kHeadsPerCta + h;
         if (hg >= p.group) continue;
@@ -603,6 +654,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     }
     __syncthreads();
     need_proxy_fence = true;
+    if (!Policy::PIPELINED && deferred_issue) issue_next();
 
     if constexpr (!kMulti) {
       break;
@@ -689,8 +741,11 @@ inline int make_row_map(CUtensorMap* tm, const void* base, int64_t rows, int row
   return TKV_OK;
 }
 
-template <class Policy>
+// MODES: bit m set = schedule mode m (1, 2, 3) is built for this policy.
+template <class Policy, int MODES = 0xE>
 struct SplitLaunch {
+  static constexpr bool kHas1 = (MODES & 2) != 0, kHas2 = (MODES & 4) != 0, kHas3 = (MODES & 8) != 0;
+  static_assert(kHas1 || kHas2 || kHas3, "no schedule mode selected");
   static int smem_bytes() {
     return Policy::WARPS * Policy::STAGES * Policy::STAGE_BYTES + Policy::WARPS * Policy::STAGES * 8 +
            16 + 2 * kHeadsPerCta * Policy::D * 4 +  // query barriers and the two query slots
@@ -700,16 +755,24 @@ struct SplitLaunch {
   static constexpr int kPrefixBytes = (kMaxRaggedB + 1) * 4 + 32;  // ragged batches: tile prefix
   template <int MODE>
   static const void* fn_mode() { return reinterpret_cast<const void*>(&splitk_kernel<Policy, MODE>); }
-  static const void* fn() { return fn_mode<1>(); }  // same launch bounds and shared memory in all modes
+  // same launch bounds and shared memory in all modes: any built one answers for the family
+  static const void* fn() {
+    if constexpr (kHas1) return fn_mode<1>();
+    else if constexpr (kHas2) return fn_mode<2>();
+    else return fn_mode<3>();
+  }
   static int prepare() {
     static bool done[64] = {};
     int dev = 0;
     TKV_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && done[dev]) return TKV_OK;
-    TKV_CUDA(cudaFuncSetAttribute(fn_mode<1>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
-    TKV_CUDA(cudaFuncSetAttribute(fn_mode<2>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
-    TKV_CUDA(cudaFuncSetAttribute(fn_mode<3>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  smem_bytes() + kPrefixBytes));
+    if constexpr (kHas1)
+      TKV_CUDA(cudaFuncSetAttribute(fn_mode<1>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    if constexpr (kHas2)
+      TKV_CUDA(cudaFuncSetAttribute(fn_mode<2>(), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes()));
+    if constexpr (kHas3)
+      TKV_CUDA(cudaFuncSetAttribute(fn_mode<3>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    smem_bytes() + kPrefixBytes));
     if (dev < 64) done[dev] = true;
     return TKV_OK;
   }
@@ -739,7 +802,7 @@ struct SplitLaunch {
     int rc = wave(&w);
     if (rc != TKV_OK) return rc;
     *sc = make_sched(B, HKV, hchunks, S, num_splits, split_size, ragged, w, Policy::TOK,
-                     Policy::WARPS);
+                     Policy::WARPS, kHas2);
     return TKV_OK;
   }
   static int launch(const typename Policy::Maps& maps, const DecodeParams& p, const SplitSched& sc,
@@ -754,19 +817,29 @@ struct SplitLaunch {
     // replay a dependent launch placed one CTA per still-resident combine CTA late (by
     // 10-30 us at batch 16-32), which the static tile ranges cannot absorb.
     const dim3 grid(sc.grid), block(Policy::WARPS * 32);
-    if (sc.persistent == 2) {
-      TKV_CUDA(launch_pdl(splitk_kernel<Policy, 2>, grid, block, (size_t)smem_bytes(), stream, maps, p, sc));
+    if (sc.persistent == 1) {
+      if constexpr (kHas1) {
+        splitk_kernel<Policy, 1><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
+        TKV_CUDA(cudaGetLastError());
+        return TKV_OK;
+      }
+    } else if (sc.persistent == 3) {
+      if constexpr (kHas3) {
+        splitk_kernel<Policy, 3><<<grid, block, smem_bytes() + kPrefixBytes, stream>>>(maps, p, sc);
+        TKV_CUDA(cudaGetLastError());
+        return TKV_OK;
+      }
+    } else if constexpr (kHas2) {
+      if (sc.persistent == 2) {
+        TKV_CUDA(launch_pdl(splitk_kernel<Policy, 2>, grid, block, (size_t)smem_bytes(), stream, maps, p, sc));
+      } else {
+        splitk_kernel<Policy, 2><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
+        TKV_CUDA(cudaGetLastError());
+      }
       return TKV_OK;
     }
-    if (sc.persistent == 1) {
-      splitk_kernel<Policy, 1><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
-    } else if (sc.persistent == 3) {
-      splitk_kernel<Policy, 3><<<grid, block, smem_bytes() + kPrefixBytes, stream>>>(maps, p, sc);
-    } else {
-      splitk_kernel<Policy, 2><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
-    }
-    TKV_CUDA(cudaGetLastError());
-    return TKV_OK;
+    set_error("split kernel: schedule mode %d is not built for this kernel family", sc.persistent);
+    return TKV_ERR_INVALID;
   }
   static int attrs(int* regs, int* smem, int* local, int* ctas) {
     int rc = prepare();

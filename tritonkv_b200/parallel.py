@@ -188,6 +188,17 @@ class PeerExchange:
         a = scratch["acc"]
         self.push(a.view(1, self.rows, 1, self.D) if a.dim() == 3 else a, scratch["m"], scratch["l"])
 
+    def exchange(self, acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor,
+                 out: torch.Tensor) -> torch.Tensor:
+        """:meth:`push` and :meth:`wait_merge` as one kernel launch."""
+        NS = acc.shape[2]
+        with torch.cuda.device(acc.device):
+            _cabi.check(_cabi.load().tkv_combine_exchange(
+                acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(), self.rows, NS, self.D,
+                NS * self.D, self.D, NS, 1, self.data_ptrs, self.state_ptr, self.world, self.rank,
+                self.wire, _cabi.stream_ptr(acc.device)))
+        return out
+
     def wait_merge(self, out: torch.Tensor) -> torch.Tensor:
         with torch.cuda.device(out.device):
             _cabi.check(_cabi.load().tkv_merge_wait(
@@ -254,11 +265,10 @@ class HistorySplitDecoder:
 
             if kq is None or kq.packed.shape[2] == 0:
                 self.peer.push_empty(self._empty, self.out.device)
-            else:
-                fused_decode_attention(q, kq, vq, sm_scale=sm_scale, _workspace=self.ws,
-                                       _partials_only=True, out=self.out)
-                self.peer.push(self.ws["acc"], self.ws["maxs"], self.ws["sums"])
-            return self.peer.wait_merge(self.out)
+                return self.peer.wait_merge(self.out)
+            fused_decode_attention(q, kq, vq, sm_scale=sm_scale, _workspace=self.ws,
+                                   _partials_only=True, out=self.out)
+            return self.peer.exchange(self.ws["acc"], self.ws["maxs"], self.ws["sums"], self.out)
         self.local_partial(q, kq, vq, sm_scale)
         gather_partials(self.local, self.group, out=self.gathered)
         return merge_gathered(self.gathered, self.B, self.HQ, self.D, out=self.out)
