@@ -437,13 +437,12 @@ def multi_gpu_parity(cx):
     cut = lambda t: Q.QuantizedTensor(t.packed[:, :, lo:hi].contiguous(), t.scale[:, :, lo:hi].contiguous(),
                                       t.zero[:, :, lo:hi].contiguous(), 2, GS, D)
     kq_l, vq_l = cut(kq), cut(vq)
-    ref_rep = None
     for exchange in ("peer", "nccl"):
         key = f"history_split_{exchange}"
         try:
             dec = P.HistorySplitDecoder(1, HQ, D, cx.device, exchange=exchange)
-        except RuntimeError as exc:
-            res[key] = f"unavailable: {exc}"
+        except Exception as exc:  # e.g. no symmetric memory on this system: every rank raises
+            res[key] = f"unavailable: {exc!r}"[:300]
             continue
         outs = [dec.step(q, kq_l, vq_l).clone() for _ in range(3)]  # the buffers are reused per step
         torch.cuda.synchronize()
@@ -711,8 +710,6 @@ def run_ours(args):
                            "speedup_hot": c_hot["median_ms"] / hot["median_ms"],
                            "byte_ratio": cell["bytes16"] / cbytes})
         if nbits == 4 and name != "ragged-b16":
-            for r in cell["reps"]:  # the 2-bit caches are quantised from the same values where they are kept
-                r.pop("kq", None), r.pop("vq", None)
             c2 = fused_cell(cx, name, B_loc, S_loc, 2, seed, b_lo=b_lo)
             s2 = cx.time_steps(c2["step"])
             s2s = cx.time_steps(c2["split"])
@@ -745,6 +742,31 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_table and name in ("llama8b-b64", "qwen-b1"):
         rows = sweep_rows(cx, (2048, 8192, 16384, 65536), args.seed)
 
+    # ---- the reference's Triton kernels, JIT-compiled on this GPU (rank 0, one GPU) ----
+    triton = None
+    if rank == 0 and world == 1 and not args.light and not args.no_table:
+        torch.cuda.empty_cache()
+        cells = [{"B": B_loc, "HQ": HQ, "HKV": HKV, "S": S_loc, "D": D, "nbits": [4, 2], "gs": GS,
+                  "dist": WORKLOADS[name][6]}] if name == "llama8b-b64" else []
+        qB, qHQ, qHKV, qD = WORKLOADS["qwen-b1"][:4]
+        cells += [{"B": qB, "HQ": qHQ, "HKV": qHKV, "S": c, "D": qD, "nbits": [4, 2], "gs": GS,
+                   "dist": "channel"} for c in sorted({r["ctx"] for r in rows})]
+        tr, why = triton_rows(cells)
+        triton = {"rows": tr, "unavailable": why,
+                  "what": "the reference's fused_decode_attention / fp16_decode_attention (Triton, JIT on "
+                          "this GPU) under the same hot / cold graph protocol, in a separate process"}
+        for t in tr or []:  # next to our own numbers of the same cell
+            for r in rows:
+                if (r["ctx"], qB, qHQ) == (t["S"], t["B"], t["HQ"]):
+                    r["triton_fused_cold_us"] = t.get(f"triton_fused_{r['nbits']}b_cold_us")
+                    r["triton_fused_hot_us"] = t.get(f"triton_fused_{r['nbits']}b_hot_us")
+                    r["triton_fp16_cold_us"] = t.get("triton_fp16_cold_us")
+                    r["triton_fp16_hot_us"] = t.get("triton_fp16_hot_us")
+            if name == "llama8b-b64" and (t["B"], t["S"], t["HQ"]) == (B_loc, S_loc, HQ) and extras:
+                extras["triton_fused_cold_us"] = t.get(f"triton_fused_{nbits}b_cold_us")
+                extras["triton_fused_2bit_cold_us"] = t.get("triton_fused_2b_cold_us")
+                extras["triton_fp16_cold_us"] = t.get("triton_fp16_cold_us")
+
     clocks = sampler.stop()
 
     # ---- CPU baseline on this box's host cores (rank 0, single GPU only) ----
@@ -773,7 +795,7 @@ def run_ours(args):
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * K, "clocks": clocks, "parity_vs_oracle": parity,
-            "same_shape": extras, "history_split": hist, "rows": rows,
+            "same_shape": extras, "history_split": hist, "rows": rows, "reference_triton": triton,
         }
         print(json.dumps(line), flush=True)
     teardown(cx)
@@ -917,6 +939,32 @@ def sweep_rows(cx, contexts, seed, nbits_list=(4, 2), name="qwen-b1"):
             })
         torch.cuda.empty_cache()
     return rows
+
+
+def triton_rows(cells, timeout_s=900):
+    """The reference's own Triton kernels on this GPU, timed by ``baseline/triton_leg.py`` in a
+    separate process (it imports the reference's modules from the git-ignored
+    ``baseline/_ref``, placed there by ``baseline/fetch_ref.py``; this process never imports
+    them).  Returns (rows, reason): rows is None with a reason when the leg cannot run."""
+    import subprocess
+
+    leg = os.path.join(ROOT, "baseline", "triton_leg.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref")):
+        return None, "baseline/_ref is absent: the reference's modules were not placed on this box"
+    try:
+        r = subprocess.run([sys.executable, leg, json.dumps(cells)], capture_output=True, text=True,
+                           timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return None, f"the Triton leg did not finish in {timeout_s} s"
+    if r.returncode != 0:
+        return None, "the Triton leg failed: " + r.stderr.strip().splitlines()[-1][:300] if r.stderr.strip() else "the Triton leg failed"
+    try:
+        res = json.loads(r.stdout.strip().splitlines()[-1])
+    except Exception as exc:
+        return None, f"unreadable output of the Triton leg: {exc!r}"
+    if isinstance(res, dict):
+        return None, res.get("unavailable", "unavailable")
+    return res, None
 
 
 L2_SWEEP_FACTORS = (0.125, 0.25, 0.5, 1.0, 2.0, 4.0, 8.0, 12.0)

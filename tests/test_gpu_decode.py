@@ -477,6 +477,27 @@ def test_llama70b_long_context_full_size():
     assert_close(got, ref, "llama-70b ctx 131072 2-bit")
 
 
+def test_long_context_sweep_top_context_against_oracle():
+    """The longest context of the reference's long-context sweep (ctx 393216, Qwen2.5-1.5B
+    head layout, 4-bit; docs/preregistration_l2.md:36-38 of the reference), fused kernel and
+    fp16 control, against the C twin of the memory-frugal grouped oracle
+    (l2_sweep.py:196-236)."""
+    from oracle import c_oracle
+
+    B, HQ, HKV, S, D = 1, 12, 2, 393216, 128
+    g = torch.Generator(device=DEV).manual_seed(31)
+    q = torch.randn(B, HQ, D, generator=g, device=DEV).half()
+    k = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    v = torch.randn(B, HKV, S, D, generator=g, device=DEV).half()
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    c_oracle.use_all_cores()
+    assert_close(fused_decode_attention(q, kq, vq), c_oracle_attention(q, kq, vq), "ctx 393216 4-bit")
+    got16 = fp16_decode_attention(q, k, v)
+    ref16 = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
+                                         v.float().cpu().numpy())
+    assert_close(got16, ref16, "ctx 393216 fp16 control")
+
+
 @pytest.mark.parametrize("nbits", [4, 2])
 def test_llama8b_batch64_full_size_against_oracle(nbits):
     """Llama-3-8B-shaped decode at its full size (batch 64, HQ 32 / HKV 8, ctx 4096): the
