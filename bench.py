@@ -525,9 +525,10 @@ def history_split_record(cx, seed):
         dec = P.HistorySplitDecoder(B, HQ, D, cx.device)
         steps = [(lambda r=r: dec.step(r["q"], r["kq"], r["vq"])) for r in reps]
         out_dev = dec.out
-        rec["exchange"] = ("stores into peer memory, tagged {value, step} pairs" if dec.exchange == "peer"
-                           else "one NCCL all-gather")
-        launches = 3
+        rec["exchange"] = ("stores into peer memory, tagged {value, step} pairs, one kernel"
+                           if dec.exchange == "peer" else "one NCCL all-gather")
+        # split kernel + the exchange kernel; with NCCL: split, local merge, all-gather, merge
+        launches = 2 if dec.exchange == "peer" else 4
     else:
         out_dev = torch.empty(B, HQ, D, device=cx.device)
         ws: dict = {}
@@ -856,19 +857,42 @@ def e2e_leg(cx, name, B, HQ, D, nbits, seed, b_lo, S, seq_lens, valid_frac, tota
         raise RuntimeError("graphed step and direct call disagree")
     ms_graphed = h.stats([cx.max_over_ranks(h.time_region(lambda: graphed(K_e2e), cx.barrier))
                           for _ in range(n_s)])["median_ms"]
-    ms_e2e = min(ms_graphed, ms_direct)
+    # The same graph without the copy nodes: the kernels read q from and write out to the pinned
+    # host buffers themselves (GraphedDecodeStep(zero_copy=True)); the bytes that cross the bus
+    # per step are the same.
+    zsteps = [GraphedDecodeStep(r["kq"], r["vq"], HQ, q_dtype=r["q"].dtype, seq_lens=seq_lens,
+                                zero_copy=True) for r in reps]
+    for g, qh in zip(zsteps, q_host):
+        g.q_host.copy_(qh)
+
+    def zero_copy(n):
+        for i in range(n):
+            g = zsteps[i % R]
+            g.run()
+            g.result()
+
+    zero_copy(min(50, K_e2e))
+    zsteps[0].run(q_host[0])
+    if not torch.equal(zsteps[0].result(), out_dev.cpu()):
+        raise RuntimeError("zero-copy step and direct call disagree")
+    ms_zero = h.stats([cx.max_over_ranks(h.time_region(lambda: zero_copy(K_e2e), cx.barrier))
+                       for _ in range(n_s)])["median_ms"]
+    ms_e2e = min(ms_graphed, ms_direct, ms_zero)
+    path = {ms_graphed: "graphed", ms_direct: "direct", ms_zero: "graphed, zero-copy"}[ms_e2e]
     return {"value": total_bytes * K_e2e / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
             "h2d_bytes_per_step": int(q_dev.numel() * q_dev.element_size()),
             "d2h_bytes_per_step": int(out_host.numel() * 4), "steps": K_e2e,
             "us_per_step": ms_e2e * 1e3 / K_e2e,
-            "path": "graphed" if ms_graphed <= ms_direct else "direct",
+            "path": path,
             "graphed_us_per_step": ms_graphed * 1e3 / K_e2e,
+            "zero_copy_us_per_step": ms_zero * 1e3 / K_e2e,
             "direct_call_us_per_step": ms_direct * 1e3 / K_e2e,
             "note": "per step: q pinned-host->device, fused_decode_attention (split + combine), "
                     "out device->pinned-host, stream sync; the KV cache is resident state. "
                     "graphed: tritonkv_b200.GraphedDecodeStep (the copies and kernels captured as "
-                    "one CUDA graph, one launch per step); direct: the same four host calls "
-                    f"issued one by one; value = the faster of the two; median of {n_s} regions"}
+                    "one CUDA graph, one launch per step); zero-copy: the same graph without copy nodes, "
+                    "the kernels read q from and write out to pinned host memory themselves; direct: the "
+                    f"four host calls issued one by one; value = the fastest; median of {n_s} regions"}
 
 
 def teardown(cx):

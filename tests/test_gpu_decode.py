@@ -597,6 +597,28 @@ def test_graphed_decode_step_equals_direct_calls_and_follows_the_cache():
     assert_close(step.result(), oracle_attention(q.to(DEV), dense[0], dense[1]), "after 40 appends")
 
 
+@pytest.mark.parametrize("B,HQ,HKV,S", [(1, 12, 2, 8192), (4, 32, 8, 1000), (1, 12, 2, 17)])
+def test_zero_copy_graphed_step_equals_the_copying_one(B, HQ, HKV, S):
+    """GraphedDecodeStep(zero_copy=True): the kernels read the query from pinned host memory
+    and write the result into pinned host memory themselves (no copy nodes in the graph);
+    same bits as the copying form and as the direct call, step after step."""
+    from tritonkv_b200 import GraphedDecodeStep
+
+    q0, k, v = make_random_kv(B, HQ, HKV, S, 128, device=DEV, seed=41)
+    kq, vq = Q.quantize_kv(k, v, 4, 32)
+    zc = GraphedDecodeStep(kq, vq, HQ, zero_copy=True)
+    cp = GraphedDecodeStep(kq, vq, HQ)
+    g = torch.Generator().manual_seed(5)
+    for _ in range(4):
+        q = torch.randn(B, HQ, 128, generator=g).half()
+        zc.run(q)
+        a = zc.result().clone()
+        cp.run(q)
+        b = cp.result().clone()
+        assert torch.equal(a, b)
+        assert torch.equal(a, fused_decode_attention(q.to(DEV), kq, vq).cpu())
+
+
 def test_combine_flag_equals_two_calls_through_the_c_abi():
     """TKV_FLAG_COMBINE (split kernel + combine enqueued by one call) gives the bits of
     tkv_fused_decode followed by tkv_combine."""

@@ -49,6 +49,7 @@ def fused_decode_attention(
     _workspace: dict | None = None,
     seq_lens: torch.Tensor | None = None,
     _partials_only: bool = False,
+    _host_io: bool = False,
 ) -> torch.Tensor:
     """Single decode step of attention, computed directly on packed low-bit K/V.
 
@@ -69,6 +70,9 @@ def fused_decode_attention(
     follow the reference: when both are supplied the call allocates nothing and is
     CUDA-graph capturable.  ``seq_lens`` (int32 ``(B,)``, optional, no reference
     counterpart) limits sequence ``b`` to its first ``seq_lens[b]`` cached tokens.
+    ``_host_io`` (used by :class:`tritonkv_b200.GraphedDecodeStep`): ``q`` and ``out`` are
+    pinned host tensors that the kernels read and write in place over the bus -- no copy
+    is enqueued; ``out`` is then required.
     """
     ok, why = triton_available()
     if not ok:
@@ -91,10 +95,16 @@ def fused_decode_attention(
         raise ValueError(f"head_dim {D} must be a multiple of group_size {kq.group_size}")
     if fold_zp and kq.group_size < 16:
         raise ValueError(f"fold_zp needs group_size >= 16, got {kq.group_size}")
-    _cabi.require_cuda(q, "q")
     _cabi.require_cuda(kq.packed, "kq.packed")
-
-    device = q.device
+    if _host_io:
+        if out is None or not (q.is_pinned() and out.is_pinned()):
+            raise ValueError("_host_io needs pinned host tensors for q and out")
+        if out.shape != (B, HQ, D) or out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous float32 tensor of shape {(B, HQ, D)}")
+        device = kq.packed.device
+    else:
+        _cabi.require_cuda(q, "q")
+        device = q.device
     check_cache_tensors(kq, "kq", device)
     check_cache_tensors(vq, "vq", device)
     sm_scale = 1.0 / math.sqrt(D) if sm_scale is None else sm_scale
@@ -116,7 +126,8 @@ def fused_decode_attention(
         nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S,
                                       num_splits, split_size, ragged)
 
-        out = check_out(out, B, HQ, D, device)
+        if not _host_io:
+            out = check_out(out, B, HQ, D, device)
         ws = _workspace if _workspace is not None else {}
         acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
 

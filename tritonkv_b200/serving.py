@@ -23,11 +23,19 @@ class GraphedDecodeStep:
     :meth:`run`, then :meth:`result` to wait for and get the step's output.  The cache
     tensors must stay where they were at capture (append in place with
     ``quantize.append_kv`` and grow ``seq_lens`` on the device to lengthen the history).
+
+    ``zero_copy=True`` takes the two copies off the step: the split kernel fetches the query
+    rows straight from ``q_host`` and the last kernel of the step stores the result straight
+    into ``out_host`` (pinned host memory is addressable from the device), so the graph holds
+    the kernels only.  It pays while the query and the result are small against the bus
+    latency of a copy node (a few KB at batch 1); large batches are better served by the
+    copy engines.
     """
 
     def __init__(self, kq: QuantizedTensor, vq: QuantizedTensor, HQ: int,
                  q_dtype: torch.dtype = torch.float16, seq_lens: torch.Tensor | None = None,
-                 sm_scale: float | None = None, num_splits: int | None = None):
+                 sm_scale: float | None = None, num_splits: int | None = None,
+                 zero_copy: bool = False):
         dev = kq.packed.device
         if dev.type != "cuda":
             raise RuntimeError("GraphedDecodeStep needs a CUDA cache; this package has no CPU path")
@@ -40,7 +48,14 @@ class GraphedDecodeStep:
         self._dev = dev
         self._stream = torch.cuda.Stream(device=dev)  # capture stream only
 
+        self.zero_copy = zero_copy
+
         def step():
+            if zero_copy:
+                fused_decode_attention(self.q_host, kq, vq, sm_scale=sm_scale, num_splits=num_splits,
+                                       out=self.out_host, _workspace=self._ws, seq_lens=seq_lens,
+                                       _host_io=True)
+                return
             self.q_dev.copy_(self.q_host, non_blocking=True)
             fused_decode_attention(self.q_dev, kq, vq, sm_scale=sm_scale, num_splits=num_splits,
                                    out=self.out_dev, _workspace=self._ws, seq_lens=seq_lens)
