@@ -43,12 +43,14 @@ extern "C" {
 /* flags for the two decode entry points */
 #define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when nslots == 1 */
 #define TKV_FLAG_COMBINE 2       /* with nslots > 1: enqueue tkv_combine(acc, m, l -> out) after the split kernel */
+#define TKV_FLAG_K_PER_CHANNEL 4 /* tkv_fused_decode: k_scale/k_zero are (B, HKV, S/32, D), see tkv_quantize_keys_per_channel */
 
 /* kernel ids for tkv_kernel_attrs */
 #define TKV_KERNEL_FUSED_SPLIT 0
 #define TKV_KERNEL_FP16_SPLIT 1
 #define TKV_KERNEL_COMBINE 2
 #define TKV_KERNEL_QUANTIZE_PACK 3
+#define TKV_KERNEL_FUSED_SPLIT_KCHAN 4 /* the fused split kernel on per-channel keys (plans only) */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int tkv_version(void);
@@ -171,6 +173,20 @@ int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t* k_packed,
 int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed, void* scale, void* zero, int B,
                         int HKV, int T_new, int64_t S_cap, int D, int nbits, int gs,
                         const int32_t* positions, int pos0, void* stream);
+
+/* Keys quantised per channel: groups of 32 consecutive tokens of ONE head dimension, the
+ * format the reference describes as future work (docs/future_work.md:229-293: channels that
+ * are large for every token get their own scale, which makes 2-bit keys usable) and does
+ * not implement -- no reference counterpart.  x (BH, S, D) keys of BH = B*HKV sequences x
+ * heads; the first S_q tokens (a multiple of 32, S_q <= S) of each are quantised with the
+ * per-element arithmetic of tkv_quantize_pack on the token axis: packed (BH, S_q, D*nbits/8)
+ * in the same split-P byte layout, scale / zero (BH, S_q/32, D) f16.  The last S - S_q tokens
+ * (a group that is not full yet) are left to the caller, who keeps them in f16.
+ * tkv_fused_decode reads this format when given TKV_FLAG_K_PER_CHANNEL (values stay
+ * per-token with group_size 32; S = S_q, one split, no seq_lens); the f16 tail goes through
+ * tkv_fp16_decode and tkv_combine_strided merges the two partial results. */
+int tkv_quantize_keys_per_channel(const void* x, int in_dtype, uint8_t* packed, void* scale, void* zero,
+                                  int64_t BH, int64_t S, int64_t S_q, int D, int nbits, void* stream);
 
 /* Cross-GPU exchange for a history split over the GPUs of one node (no reference
  * counterpart: the reference is single-GPU).  Each rank owns a receive buffer of

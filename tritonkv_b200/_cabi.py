@@ -25,7 +25,9 @@ TKV_ERR_ALIGN = 4
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 FLAG_PARTIALS_ONLY = 1
 FLAG_COMBINE = 2
+FLAG_K_PER_CHANNEL = 4
 KERNEL_FUSED_SPLIT, KERNEL_FP16_SPLIT = 0, 1
+KERNEL_FUSED_SPLIT_KCHAN = 4
 
 _TORCH_DTYPE = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32}
 
@@ -66,6 +68,8 @@ SIGNATURES = {
                                  c_void_p]),
     "tkv_merge_wait": (c_int, [c_void_p, c_int64, c_int, POINTER(c_void_p), c_void_p, c_int, c_int,
                                c_int, c_void_p]),
+    "tkv_quantize_keys_per_channel": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                              c_int64, c_int64, c_int, c_int, c_void_p]),
     "tkv_combine_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                      c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p), c_void_p,
                                      c_int, c_int, c_int, c_void_p]),

@@ -23,7 +23,7 @@ int fused_device_status_clear();
 int fp16_device_status_clear();
 int exchange_device_status_clear();
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
-               int num_splits, int split_size, bool ragged);
+               int num_splits, int split_size, bool ragged, bool kchan);
 int fp16_plan(int D, SplitSched* sc, int B, int HKV, int hchunks, int S, int num_splits,
               int split_size, bool ragged);
 
@@ -81,8 +81,9 @@ extern "C" int tkv_decode_plan(int kernel_id, int nbits, int D, int gs, int B, i
   const int hchunks = (HQ / HKV + kHeadsPerCta - 1) / kHeadsPerCta;
   SplitSched sc;
   int rc;
-  if (kernel_id == TKV_KERNEL_FUSED_SPLIT)
-    rc = fused_plan(nbits, D, gs, &sc, B, HKV, hchunks, S, num_splits, split_size, ragged != 0);
+  if (kernel_id == TKV_KERNEL_FUSED_SPLIT || kernel_id == TKV_KERNEL_FUSED_SPLIT_KCHAN)
+    rc = fused_plan(nbits, D, gs, &sc, B, HKV, hchunks, S, num_splits, split_size, ragged != 0,
+                    kernel_id == TKV_KERNEL_FUSED_SPLIT_KCHAN);
   else if (kernel_id == TKV_KERNEL_FP16_SPLIT)
     rc = fp16_plan(D, &sc, B, HKV, hchunks, S, num_splits, split_size, ragged != 0);
   else {

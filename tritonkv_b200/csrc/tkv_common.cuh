@@ -181,6 +181,11 @@ __device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
 // Load element `i` of a query row of any supported dtype, rounded to f16 exactly
 // as the reference's `.to(tl.float16)` does, returned as float.
 __device__ __forceinline__ __half load_q_half(const void* q, int dtype, int64_t i) {

@@ -119,10 +119,17 @@ __device__ __forceinline__ __half2 meta_bcast(const MetaRow<NG>& r, int i) {
 // instantiation serves caches whose rows start on smaller boundaries; keeping the two apart
 // keeps each kernel's instruction footprint small (a decode kernel usually starts with a
 // cold instruction cache, and the copy code is inlined at three places).
+// KCHAN: the K scale/zero arrays hold one row of D values per block of kTok tokens (keys
+// quantised per channel over groups of kTok tokens) instead of D/GS values per token.  With
+// GS == kTok both forms fill the same bytes of a stage, so only the source address of the two
+// K metadata copies and the score arithmetic differ.
 template <int NBITS, int D_, int GS, bool A16 = true, int TOK_ = 32, int WARPS_ = 4, int STAGES_ = 3,
-          int MIN_CTAS_ = 3, bool PIPELINED_ = true>
+          int MIN_CTAS_ = 3, bool PIPELINED_ = true, bool KCHAN_ = false>
 struct FusedPolicy {
   using C = FusedCfg<NBITS, D_, GS, TOK_>;
+  static constexpr bool KCHAN = KCHAN_;
+  static_assert(!KCHAN || (GS == TOK_ && A16 && D_ / GS > 1),
+                "per-channel keys: value groups of one tile's tokens, 16-byte aligned rows");
   static constexpr int D = D_;
   static constexpr int kTok = C::kTok, MT = C::MT;
   static constexpr int TOK = kTok;
@@ -167,6 +174,7 @@ struct FusedPolicy {
   static constexpr int ROUNDS = (4 * CPA + 31) / 32;               // cp.async rounds per tile
   struct IssueState {
     const uint8_t* src[ROUNDS];  // this lane's source of round r at global row 0
+    bool is_k[ROUNDS];           // the chunk belongs to the K scale or zero array
   };
   __device__ static __forceinline__ void issue_init(IssueState& is, const DecodeParams& p, int lane) {
 #pragma unroll
@@ -175,6 +183,7 @@ struct FusedPolicy {
       const int arr = (i / CPA) & 3, c = i % CPA;
       const __half* base = arr == 0 ? p.ks : arr == 1 ? p.kz : arr == 2 ? p.vs : p.vz;
       is.src[r] = reinterpret_cast<const uint8_t*>(base) + c * 16;
+      is.is_k[r] = arr < 2;
     }
   }
 
@@ -198,12 +207,14 @@ struct FusedPolicy {
     if constexpr (A16) {
       if (NG == 1 && lane == 0)  // no read-back shift (see FusedCfg::META_STRIDE)
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(mst + C::SHIFT_WORD), "r"(0u) : "memory");
-      if (NG > 1 && nvalid == kTok) {
+      if (KCHAN || (NG > 1 && nvalid == kTok)) {
         const int64_t off = (int64_t)row * (NG * 2);  // bytes
+        // per-channel keys: one (D,) row per tile; tiles start on multiples of kTok tokens
+        const int64_t off_k = KCHAN ? (int64_t)(row / kTok) * (D * 2) : off;
 #pragma unroll
         for (int r = 0; r < ROUNDS; ++r) {
           if (4 * CPA >= 32 || lane < 4 * CPA)
-            cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + off, 16);
+            cp_async16(mst + (r * 32 + lane) * 16, is.src[r] + ((KCHAN && is.is_k[r]) ? off_k : off), 16);
         }
         cp_async_mbar_arrive_noinc(bar);
       } else {
@@ -390,9 +401,98 @@ struct FusedPolicy {
 
   // Scores of one tile in stage `st` (scaled by qk_scale, tokens past the unit
   // end set to -inf); `left` = tokens from the tile start to the unit end.
+  // Per-channel keys: K = code * s[d] + z[d] with one (s, z) row for the whole tile, so
+  //     q.k_n = sum_d (q_d s_d) c_{n,d} + sum_d q_d z_d.
+  // The scale goes into the B operand (q' = q * s, formed once per tile in f16), all chunks
+  // share ONE accumulator, and the zero-point term -- the same for every token of the tile --
+  // is one MMA per chunk whose A operand is the z row repeated down the token rows.
+  __device__ static __forceinline__ void scores_kchan(Scores& out, const Query& qq, uint32_t st,
+                                                      int left, float qk_scale, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t kc = st;
+    const uint32_t ms = st + 2 * C::CODE_BYTES;
+    const uint32_t ks_r = ms + t * 8;                     // dims 16ch + 4t .. 16ch + 4t + 3 of a chunk
+    const uint32_t kz_r = ms + C::META_STRIDE + t * 8;
+    const float qk24 = qk_scale * 16777216.f;  // the code fields carry 2^-24
+    uint32_t qs[NCH][2];
+    float cz[4];
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const uint2 sv = lds_v2(ks_r + ch * 32);
+      const uint2 zv = lds_v2(kz_r + ch * 32);
+      // k-slots 2t, 2t+1 <-> dims 16ch+4t, 16ch+4t+2; k-slots 2t+8, 2t+9 <-> dims +1, +3
+      const uint32_t s02 = __byte_perm(sv.x, sv.y, 0x5410), s13 = __byte_perm(sv.x, sv.y, 0x7632);
+      uint32_t z02 = __byte_perm(zv.x, zv.y, 0x5410), z13 = __byte_perm(zv.x, zv.y, 0x7632);
+      qs[ch][0] = hmul2_u32(qq.qf[ch][0], s02);
+      qs[ch][1] = hmul2_u32(qq.qf[ch][1], s13);
+      // the query of bit slice p carries 2^(-NBITS p): the zero row of that slice takes it back
+      const int slice = ch / NBLK;
+      if (slice > 0) {
+        const __half2 up2 = __float2half2_rn(pow2i(NBITS * slice));
+        const uint32_t up = *reinterpret_cast<const uint32_t*>(&up2);
+        z02 = hmul2_u32(z02, up);
+        z13 = hmul2_u32(z13, up);
+      }
+      if (ch == 0) {
+        mma16816_zero(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
+      } else {
+        mma16816(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cz[i] *= qk_scale;
+    float (&sc)[MT][4] = out.s;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float c[4];
+      bool started = false;
+#pragma unroll
+      for (int bb = 0; bb < NBLK; bb += 2) {
+        uint32_t r[4];
+        if constexpr (NBLK >= 2) {
+          ldmatrix_x4(r, kc + qq.off[mt][bb >> 1]);
+        } else {
+          ldmatrix_x2(r[0], r[1], kc + qq.off[mt][0]);
+          r[2] = r[3] = 0;
+        }
+#pragma unroll
+        for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
+          const int blk = bb + jj;
+          const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
+          const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+#pragma unroll
+          for (int pp = 0; pp < P; ++pp) {
+            constexpr uint32_t M0 = C::MASK0;
+            const uint32_t mask = M0 << (NBITS * pp);
+            const int ch = pp * NBLK + blk;
+            if (!started) {
+              mma16816_zero(c, xl & mask, xh & mask, xl8 & mask, xh8 & mask, qs[ch][0], qs[ch][1]);
+              started = true;
+            } else {
+              mma16816(c, xl & mask, xh & mask, xl8 & mask, xh8 & mask, qs[ch][0], qs[ch][1]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[mt][i] = fmaf(c[i], qk24, cz[i]);
+    }
+    if (left < kTok) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if (mt * 16 + g >= left) sc[mt][0] = sc[mt][1] = -INFINITY;
+        if (mt * 16 + g + 8 >= left) sc[mt][2] = sc[mt][3] = -INFINITY;
+      }
+    }
+  }
+
   __device__ static __forceinline__ void scores(Scores& out, const Query& qq, uint32_t st,
                                                 const uint8_t*, int left, float qk_scale,
                                                 int lane) {
+    if constexpr (KCHAN) {
+      scores_kchan(out, qq, st, left, qk_scale, lane);
+      return;
+    }
     const int g = lane >> 2;
     const uint32_t kc = st;
     uint32_t ms = st + 2 * C::CODE_BYTES;
@@ -649,10 +749,25 @@ struct FusedPolicy {
 //    third fewer query loads and epilogues, which is what a step of 2-3 tiles per warp is
 //    made of (measured: batch 1, ctx 65536, 4-bit step 12.4 -> 10.8 us).
 constexpr int kVariantBatched = 0, kVariantLong = 1;
-template <int NB, int DD, int GG, bool A16>
-using BatchedPolicy = FusedPolicy<NB, DD, GG, A16, 32, 4, 3, 3, true>;
-template <int NB, int DD, int GG, bool A16>
-using LongPolicy = FusedPolicy<NB, DD, GG, A16, 32, 8, 2, 2, false>;
+template <int NB, int DD, int GG, bool A16, bool KCHAN = false>
+using BatchedPolicy = FusedPolicy<NB, DD, GG, A16, 32, 4, 3, 3, true, KCHAN>;
+template <int NB, int DD, int GG, bool A16, bool KCHAN = false>
+using LongPolicy = FusedPolicy<NB, DD, GG, A16, 32, 8, 2, 2, false, KCHAN>;
+
+// Keys quantised per channel (value groups of 32): dense batches only, so mode 1 and mode 2.
+#define TKV_KCHAN_DISPATCH(NB, DD, EXPR)                            \
+  if (nbits == NB && D == DD && gs == 32) {                         \
+    using PB = BatchedPolicy<NB, DD, 32, true, true>;               \
+    using PL = LongPolicy<NB, DD, 32, true, true>;                  \
+    using LB = SplitLaunch<PB, 0x2>;                                \
+    using LL = SplitLaunch<PL, 0x4>;                                \
+    return EXPR;                                                    \
+  }
+#define TKV_KCHAN_ALL(EXPR)        \
+  TKV_KCHAN_DISPATCH(4, 128, EXPR) \
+  TKV_KCHAN_DISPATCH(2, 128, EXPR) \
+  TKV_KCHAN_DISPATCH(4, 64, EXPR)  \
+  TKV_KCHAN_DISPATCH(2, 64, EXPR)
 
 #define TKV_FUSED_DISPATCH(NB, DD, GG, EXPR)                        \
   if (nbits == NB && D == DD && gs == GG) {                         \
@@ -686,6 +801,13 @@ using LongPolicy = FusedPolicy<NB, DD, GG, A16, 32, 8, 2, 2, false>;
   TKV_FUSED_DISPATCH(2, 64, 16, EXPR)   \
   TKV_FUSED_DISPATCH(2, 64, 32, EXPR)   \
   TKV_FUSED_DISPATCH(2, 64, 64, EXPR)
+
+static int kchan_unsupported(int nbits, int D, int gs) {
+  set_error("fused decode with per-channel keys: unsupported (nbits=%d, head_dim=%d, value "
+            "group_size=%d); built: nbits in {2,4}, head_dim in {64,128}, value group_size 32",
+            nbits, D, gs);
+  return TKV_ERR_UNSUPPORTED;
+}
 
 static int fused_unsupported(int nbits, int D, int gs) {
   set_error("fused decode: unsupported (nbits=%d, head_dim=%d, group_size=%d); built: nbits in "
@@ -731,14 +853,23 @@ static int fused_plan_both(SplitSched* sc, int B, int HKV, int hchunks, int S, i
 }
 
 int fused_plan(int nbits, int D, int gs, SplitSched* sc, int B, int HKV, int hchunks, int S,
-               int num_splits, int split_size, bool ragged) {
+               int num_splits, int split_size, bool ragged, bool kchan) {
+  if (kchan) {
+    TKV_KCHAN_ALL((fused_plan_both<LB, LL>(sc, B, HKV, hchunks, S, num_splits, split_size, ragged)))
+    return kchan_unsupported(nbits, D, gs);
+  }
   constexpr bool aligned16_rows = true;  // both instantiations have the same resources
   TKV_FUSED_ALL((fused_plan_both<LB, LL>(sc, B, HKV, hchunks, S, num_splits, split_size, ragged)))
   return fused_unsupported(nbits, D, gs);
 }
 
 static int fused_launch(int nbits, int D, int gs, const DecodeParams& p, const SplitSched& sc,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, bool kchan) {
+  if (kchan) {
+    TKV_KCHAN_ALL((sc.variant == kVariantLong ? fused_launch_one<LL, PL>(p, sc, stream)
+                                              : fused_launch_one<LB, PB>(p, sc, stream)))
+    return kchan_unsupported(nbits, D, gs);
+  }
   const bool aligned16_rows = p.meta_aligned == 16;
   TKV_FUSED_ALL((sc.variant == kVariantLong ? fused_launch_one<LL, PL>(p, sc, stream)
                                             : fused_launch_one<LB, PB>(p, sc, stream)))
@@ -810,14 +941,25 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
   }
   // 128-byte-row view of the code tensors: every sequence must start on a 128-byte boundary
   p.wide = (((int64_t)S * D * nbits / 8) % 128 == 0) ? 1 : 0;
+  const bool kchan = (flags & TKV_FLAG_K_PER_CHANNEL) != 0;
+  if (kchan) {
+    // k_scale / k_zero are (B, HKV, S/32, D): one row per block of 32 tokens, so every tile
+    // must be one whole block -- a history of whole blocks, one split, no per-sequence lengths
+    TKV_REQUIRE(S % 32 == 0 && num_splits == 1 && seq_lens == nullptr, TKV_ERR_INVALID,
+                "fused decode with per-channel keys: S=%d must be a multiple of 32, with one split "
+                "and no seq_lens (the fp16 tail goes through tkv_fp16_decode)", S);
+    TKV_REQUIRE(aligned16(k_scale) && aligned16(v_scale), TKV_ERR_ALIGN,
+                "fused decode with per-channel keys: scale/zero pointers must be 16-byte aligned");
+    p.meta_aligned = 16;
+  }
   SplitSched sc;
   rc = fused_plan(nbits, D, gs, &sc, B, HKV, p.hchunks, S, num_splits, split_size,
-                  seq_lens != nullptr);
+                  seq_lens != nullptr, kchan);
   if (rc != TKV_OK) return rc;
   TKV_REQUIRE(sc.nslots == nslots, TKV_ERR_INVALID,
               "fused decode: nslots=%d does not match the plan (%d); size acc/m/l with "
               "tkv_decode_plan", nslots, sc.nslots);
-  rc = fused_launch(nbits, D, gs, p, sc, (cudaStream_t)stream);
+  rc = fused_launch(nbits, D, gs, p, sc, (cudaStream_t)stream, kchan);
   if (rc != TKV_OK) return rc;
   if ((flags & TKV_FLAG_COMBINE) && nslots > 1 && !(flags & TKV_FLAG_PARTIALS_ONLY)) {
     TKV_REQUIRE(out, TKV_ERR_INVALID, "fused decode: TKV_FLAG_COMBINE needs out");

@@ -134,6 +134,74 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ---------------------------------------------------------------- per-channel keys
+// Keys quantised per channel: a group is kChanTok consecutive tokens of ONE head dimension
+// (the reference describes the format as future work, docs/future_work.md:229-293, and has
+// no implementation of it).  Same per-element arithmetic as quantize_pack_kernel on the other
+// axis; the codes keep the split-P byte layout along the head dimension, scale and zero are
+// one row of D values per block of kChanTok tokens.
+// One CTA per (sequence x head, token block), one thread per head dimension: the thread walks
+// the block's tokens of its dimension (the loads of a warp are one contiguous row piece),
+// derives scale/zero, leaves its codes in shared memory, and the CTA then packs whole rows.
+constexpr int kChanTok = 32;
+
+template <typename T>
+__device__ __forceinline__ float load1(const T* p) { return (float)*p; }
+template <>
+__device__ __forceinline__ float load1<__half>(const __half* p) { return __half2float(*p); }
+template <>
+__device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+
+template <typename T, int NBITS>
+__global__ void __launch_bounds__(256)
+    quantize_keys_channel_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed,
+                                 __half* __restrict__ scale, __half* __restrict__ zero,
+                                 int64_t S, int64_t S_q, int D) {
+  constexpr int P = 8 / NBITS;
+  constexpr float QMAX = float((1 << NBITS) - 1);
+  __shared__ uint8_t codes[kChanTok][256];
+  const int d = threadIdx.x;
+  const int64_t blocks_per_seq = S_q / kChanTok;
+  const int64_t bh = blockIdx.x / blocks_per_seq, tb = blockIdx.x - bh * blocks_per_seq;
+  const T* src = x + (bh * S + tb * kChanTok) * D + d;
+  float v[kChanTok];
+  float mn, mx;
+  bool has_nan = false;
+#pragma unroll
+  for (int t = 0; t < kChanTok; ++t) {
+    v[t] = load1<T>(src + (int64_t)t * D);
+    has_nan |= v[t] != v[t];
+    mn = t == 0 ? v[0] : fminf(mn, v[t]);
+    mx = t == 0 ? v[0] : fmaxf(mx, v[t]);
+  }
+  if (has_nan) mn = mx = __int_as_float(0x7fc00000);  // NaN propagates, as in the per-token quantiser
+  float sc = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
+  sc = (sc > 0.f) ? sc : 1.f;
+  const __half sc16 = __float2half_rn(sc), ze16 = __float2half_rn(mn);
+  const float scf = __half2float(sc16), zef = __half2float(ze16);
+  const int64_t mrow = (bh * blocks_per_seq + tb) * D + d;
+  scale[mrow] = sc16;
+  zero[mrow] = ze16;
+#pragma unroll
+  for (int t = 0; t < kChanTok; ++t) {
+    float c = rintf(__fdiv_rn(__fsub_rn(v[t], zef), scf));
+    c = fminf(fmaxf(c, 0.f), QMAX);
+    codes[t][d] = (uint8_t)(int)c;
+  }
+  __syncthreads();
+  // pack: byte j of a token = OR_p code[j + p*DP] << (p*NBITS); D threads write kChanTok*DP bytes
+  const int DP = D / P;
+  for (int i = threadIdx.x; i < kChanTok * DP; i += blockDim.x) {
+    const int t = i / DP, j = i - t * DP;
+    uint32_t b = 0;
+#pragma unroll
+    for (int p = 0; p < P; ++p) b |= (uint32_t)codes[t][j + p * DP] << (p * NBITS);
+    packed[((bh * S_q) + tb * kChanTok + t) * DP + j] = (uint8_t)b;
+  }
+}
+
 // ---------------------------------------------------------------- plain pack / unpack
 template <int NBITS>
 __global__ void pack_codes_kernel(const uint8_t* __restrict__ codes, uint8_t* __restrict__ packed,
@@ -359,5 +427,43 @@ extern "C" int tkv_dequantize(const uint8_t* packed, const void* scale, const vo
     case TKV_DTYPE_F32: return launch_dequant<float>(packed, scale, zero, out, rows, D, nbits, gs, s);
   }
   set_error("dequantize: bad dtype %d", out_dtype);
+  return TKV_ERR_INVALID;
+}
+
+namespace {
+template <typename T>
+int launch_keys_channel(const void* x, uint8_t* packed, void* scale, void* zero, int64_t BH, int64_t S,
+                        int64_t S_q, int D, int nbits, cudaStream_t stream) {
+  const int64_t blocks = BH * (S_q / tkv::kChanTok);
+  TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "quantize_keys_per_channel: tensor too large");
+  if (nbits == 4)
+    tkv::quantize_keys_channel_kernel<T, 4><<<(int)blocks, D, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D);
+  else
+    tkv::quantize_keys_channel_kernel<T, 2><<<(int)blocks, D, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D);
+  TKV_CUDA(cudaGetLastError());
+  return TKV_OK;
+}
+}  // namespace
+
+extern "C" int tkv_quantize_keys_per_channel(const void* x, int in_dtype, uint8_t* packed, void* scale,
+                                             void* zero, int64_t BH, int64_t S, int64_t S_q, int D,
+                                             int nbits, void* stream) {
+  TKV_REQUIRE(nbits == 2 || nbits == 4, TKV_ERR_INVALID, "nbits must be one of (2, 4), got %d", nbits);
+  TKV_REQUIRE(BH >= 0 && S >= 0 && S_q >= 0 && S_q <= S && S_q % tkv::kChanTok == 0, TKV_ERR_INVALID,
+              "quantize_keys_per_channel: the quantised part (%lld of %lld tokens) must be a multiple of "
+              "%d tokens", (long long)S_q, (long long)S, tkv::kChanTok);
+  TKV_REQUIRE(pow2(D) && D >= 32 && D <= 256, TKV_ERR_UNSUPPORTED,
+              "quantize_keys_per_channel: built for power-of-two head_dim in [32, 256], got %d", D);
+  if (BH == 0 || S_q == 0) return TKV_OK;
+  TKV_REQUIRE(x && packed && scale && zero, TKV_ERR_INVALID, "quantize_keys_per_channel: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (in_dtype) {
+    case TKV_DTYPE_F16: return launch_keys_channel<__half>(x, packed, scale, zero, BH, S, S_q, D, nbits, s);
+    case TKV_DTYPE_BF16: return launch_keys_channel<__nv_bfloat16>(x, packed, scale, zero, BH, S, S_q, D, nbits, s);
+    case TKV_DTYPE_F32: return launch_keys_channel<float>(x, packed, scale, zero, BH, S, S_q, D, nbits, s);
+  }
+  set_error("quantize_keys_per_channel: bad dtype %d", in_dtype);
   return TKV_ERR_INVALID;
 }

@@ -8,3 +8,4 @@ from .fused_decode_attn import (  # noqa: F401
     combine_splits,
 )
 from .fp16_decode_attn import fp16_decode_attention  # noqa: F401
+from .kivi_decode_attn import KiviCache, kivi_decode_attention, quantize_kv_kivi  # noqa: F401

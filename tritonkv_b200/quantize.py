@@ -228,6 +228,83 @@ def quantize_kv(
     )
 
 
+# ---------------------------------------------------------------------------------------
+# Keys quantised per channel with an fp16 residual window.  The reference describes this
+# format as future work (docs/future_work.md:229-293) and does not implement it; there is
+# no reference counterpart for anything below.
+# ---------------------------------------------------------------------------------------
+
+CHANNEL_GROUP_TOKENS = 32  # tokens per key group == tokens per kernel tile
+
+
+@dataclass
+class ChannelKeys:
+    """Keys quantised per channel: a group is 32 consecutive tokens of one head dimension.
+
+    packed: uint8 ``(B, HKV, S_q, head_dim // P)`` in the usual split-P byte layout;
+    scale, zero: float16 ``(B, HKV, S_q // 32, head_dim)``."""
+
+    packed: torch.Tensor
+    scale: torch.Tensor
+    zero: torch.Tensor
+    nbits: int
+    head_dim: int
+
+    @property
+    def tokens(self) -> int:
+        return self.packed.shape[2]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.packed, self.scale, self.zero))
+
+    def effective_bits_per_element(self) -> float:
+        """Bits per element including scale and zero: the same 32 bits per 32 elements as
+        per-token groups of 32 (4-bit -> 5.0)."""
+        return self.nbits + _META_BITS_PER_GROUP / CHANNEL_GROUP_TOKENS
+
+
+def quantize_keys_per_channel(k: torch.Tensor, nbits: int) -> tuple[ChannelKeys, torch.Tensor]:
+    """k ``(B, HKV, S, D)`` -> (keys of the first ``S_q = S - S % 32`` tokens quantised per
+    channel, the last ``S - S_q`` tokens as float16 ``(B, HKV, S - S_q, D)``).  A channel that
+    is large for every token gets its own scale instead of flattening the small channels of
+    its per-token group, which is what makes 2-bit keys usable.  One kernel launch; same
+    per-element arithmetic as :func:`quantize_groupwise`, on the token axis."""
+    _check_bits(nbits)
+    if k.dim() != 4:
+        raise ValueError(f"k must be (B, HKV, S, D), got {tuple(k.shape)}")
+    B, HKV, S, D = k.shape
+    P = 8 // nbits
+    if D % P != 0:
+        raise ValueError(f"head_dim {D} must be divisible by {P} for {nbits}-bit packing")
+    _cabi.require_cuda(k, "k")
+    lib = _cabi.load()
+    if k.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        k = k.float()
+    k = k.contiguous()
+    G = CHANNEL_GROUP_TOKENS
+    S_q = S - S % G
+    packed = torch.empty((B, HKV, S_q, D // P), dtype=torch.uint8, device=k.device)
+    scale = torch.empty((B, HKV, S_q // G, D), dtype=torch.float16, device=k.device)
+    zero = torch.empty_like(scale)
+    with torch.cuda.device(k.device):
+        _cabi.check(lib.tkv_quantize_keys_per_channel(
+            k.data_ptr(), _cabi.dtype_code(k), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
+            B * HKV, S, S_q, D, nbits, _cabi.stream_ptr(k.device)))
+    return (ChannelKeys(packed, scale, zero, nbits, D),
+            k[:, :, S_q:].to(torch.float16).contiguous())
+
+
+def dequantize_keys_per_channel(kc: ChannelKeys, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``code * scale + zero`` per (token block, dimension), evaluated in float32 then cast.
+    A utility for tests and error reports; the decode kernel never expands the codes."""
+    codes = unpack_codes(kc.packed, kc.nbits, kc.head_dim).to(torch.float32)
+    B, HKV, S_q, D = codes.shape
+    G = CHANNEL_GROUP_TOKENS
+    cg = codes.view(B, HKV, S_q // G, G, D)
+    out = cg * kc.scale.float()[:, :, :, None] + kc.zero.float()[:, :, :, None]
+    return out.view(B, HKV, S_q, D).to(dtype)
+
+
 def empty_cache(B: int, HKV: int, S_cap: int, head_dim: int, nbits: int, group_size: int,
                 device) -> QuantizedTensor:
     """A zeroed packed cache with room for ``S_cap`` tokens per (sequence, head), to be
