@@ -4,10 +4,12 @@
 
 The reference (PS12007/tritonkv) has no packaging, so "installing" it is copying the five
 modules of its decode path, unmodified: ``quantize.py``, ``reference.py`` and
-``kernels/{__init__,fused_decode_attn,fp16_decode_attn}.py``.  ``baseline/_ref/`` is never
-committed and nothing in ``tritonkv_b200/`` imports it; its one user is
-``baseline/triton_leg.py``, a separate process that ``bench.py`` starts to time the
-reference's own Triton kernels on the same GPU, next to the CUDA kernels of this package.
+``kernels/{__init__,fused_decode_attn,fp16_decode_attn}.py``, plus its correctness suite
+``test_correctness.py``.  ``baseline/_ref/`` is never committed and nothing in
+``tritonkv_b200/`` imports it; its users are ``baseline/triton_leg.py``, a separate process
+that ``bench.py`` starts to time the reference's own Triton kernels on the same GPU next to
+the CUDA kernels of this package, and ``tests/test_gpu_reference_suite.py``, which runs the
+reference's test file against the drop-in modules.
 """
 
 from __future__ import annotations
@@ -19,7 +21,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 FILES = ["quantize.py", "reference.py", "kernels/__init__.py", "kernels/fused_decode_attn.py",
-         "kernels/fp16_decode_attn.py"]
+         "kernels/fp16_decode_attn.py",
+         # the reference's own correctness suite, run unmodified through the drop-in modules
+         # of this package by tests/test_gpu_reference_suite.py
+         "test_correctness.py"]
 
 
 def fetch(ref_root: str) -> str:
