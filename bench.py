@@ -496,6 +496,31 @@ def fused_cell(cx, name, B, S, nbits, seed, b_lo=0, want_fp16=False, seq_lens=No
             "bytes": cbytes, "bytes16": fp16_bytes(B, HKV, S, D), "R": R, "R16": min(R16, R)}
 
 
+def per_channel_cell(cx, name, B, S, seed, b_lo, world):
+    """The same shape with 2-bit keys quantised per channel over 32-token groups and 2-bit
+    per-token values (``kernels.kivi_decode_attention``; the format the reference lists as
+    future work): cold step time, same byte count per token as the 2-bit per-token cache."""
+    torch, h = cx.torch, cx.harness
+    from tritonkv_b200.kernels import kivi_decode_attention, quantize_kv_kivi
+
+    _, HQ, HKV, D = WORKLOADS[name][:4]
+    cbytes = fused_bytes(B, HKV, S, D, 2)
+    R = max(2, h.replicas_for(cbytes, cx.l2))
+    reps = device_replicas(cx, name, B, S, 2, 0, R, seed, b_lo=b_lo)
+    caches = [(r["q"], quantize_kv_kivi(r.pop("k"), r.pop("v"), 2)) for r in reps]
+    outs = [torch.empty(B, HQ, D, device=cx.device) for _ in range(R)]
+    ws: dict = {}
+    fns = [(lambda q=q, c=c, o=o: kivi_decode_attention(q, c, out=o, _workspace=ws))
+           for (q, c), o in zip(caches, outs)]
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    st = cx.time_steps(fns)
+    return {"cold_us": us(st, cx.K), "GBps": cbytes * world * cx.K / (st["median_ms"] * 1e-3) / 1e9,
+            "iqr_frac": st["iqr_frac_of_median"], "launches_per_step": 2,
+            "what": "split kernel on per-channel keys + merge of its partials (no fp16 tail at this length)"}
+
+
 def us(stats, K):
     return stats["median_ms"] * 1e3 / K
 
@@ -723,6 +748,7 @@ def run_ours(args):
                 two["byte_ratio"] = cell["bytes16"] / c2["bytes"]
             extras["two_bit"] = two
             del c2
+            extras["per_channel_keys_2bit"] = per_channel_cell(cx, name, B_loc, S_loc, seed, b_lo, world)
         torch.cuda.empty_cache()
     cx.barrier()
 
@@ -857,9 +883,9 @@ def e2e_leg(cx, name, B, HQ, D, nbits, seed, b_lo, S, seq_lens, valid_frac, tota
         raise RuntimeError("graphed step and direct call disagree")
     ms_graphed = h.stats([cx.max_over_ranks(h.time_region(lambda: graphed(K_e2e), cx.barrier))
                           for _ in range(n_s)])["median_ms"]
-    # The same graph without the copy nodes: the kernels read q from and write out to the pinned
-    # host buffers themselves (GraphedDecodeStep(zero_copy=True)); the bytes that cross the bus
-    # per step are the same.
+    # The same graph without the copy nodes: the last kernel writes out to the pinned host
+    # buffer itself (GraphedDecodeStep(zero_copy=True)); the bytes that cross the bus per step
+    # are the same.
     zsteps = [GraphedDecodeStep(r["kq"], r["vq"], HQ, q_dtype=r["q"].dtype, seq_lens=seq_lens,
                                 zero_copy=True) for r in reps]
     for g, qh in zip(zsteps, q_host):
@@ -890,8 +916,8 @@ def e2e_leg(cx, name, B, HQ, D, nbits, seed, b_lo, S, seq_lens, valid_frac, tota
             "note": "per step: q pinned-host->device, fused_decode_attention (split + combine), "
                     "out device->pinned-host, stream sync; the KV cache is resident state. "
                     "graphed: tritonkv_b200.GraphedDecodeStep (the copies and kernels captured as "
-                    "one CUDA graph, one launch per step); zero-copy: the same graph without copy nodes, "
-                    "the kernels read q from and write out to pinned host memory themselves; direct: the "
+                    "one CUDA graph, one launch per step); zero-copy: the same graph without the device-to-host copy node, "
+                    "the last kernel writes out to pinned host memory itself; direct: the "
                     f"four host calls issued one by one; value = the fastest; median of {n_s} regions"}
 
 

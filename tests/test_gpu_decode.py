@@ -599,9 +599,9 @@ def test_graphed_decode_step_equals_direct_calls_and_follows_the_cache():
 
 @pytest.mark.parametrize("B,HQ,HKV,S", [(1, 12, 2, 8192), (4, 32, 8, 1000), (1, 12, 2, 17)])
 def test_zero_copy_graphed_step_equals_the_copying_one(B, HQ, HKV, S):
-    """GraphedDecodeStep(zero_copy=True): the kernels read the query from pinned host memory
-    and write the result into pinned host memory themselves (no copy nodes in the graph);
-    same bits as the copying form and as the direct call, step after step."""
+    """GraphedDecodeStep(zero_copy=True): the last kernel of the step writes the result into
+    pinned host memory itself (no device-to-host copy node in the graph); same bits as the
+    copying form and as the direct call, step after step."""
     from tritonkv_b200 import GraphedDecodeStep
 
     q0, k, v = make_random_kv(B, HQ, HKV, S, 128, device=DEV, seed=41)

@@ -28,16 +28,19 @@ def test_reference_suite_passes_through_the_dropin_modules():
     if not os.path.isfile(suite):
         pytest.skip("baseline/_ref/test_correctness.py is absent (baseline/fetch_ref.py was not run)")
     env = dict(os.environ)
-    # drop-in names first, then this repository, then the reference (for `reference`)
-    env["PYTHONPATH"] = os.pathsep.join([os.path.join(ROOT, "tritonkv_b200", "dropin"), ROOT, REF])
+    # drop-in names first, then this repository, then the reference (for `reference`).  The
+    # child runs FROM the drop-in directory: `python -m` puts the working directory at the
+    # head of sys.path, and from baseline/_ref that would be the reference's own modules.
+    dropin = os.path.join(ROOT, "tritonkv_b200", "dropin")
+    env["PYTHONPATH"] = os.pathsep.join([dropin, ROOT, REF])
     r = subprocess.run([sys.executable, "-m", "pytest", suite, "-q", "-x", "-p", "no:cacheprovider",
                         "--import-mode=importlib", "--rootdir", REF, "-k", f"not ({CPU_ONLY})"],
-                       capture_output=True, text=True, env=env, cwd=REF, timeout=1500)
+                       capture_output=True, text=True, env=env, cwd=dropin, timeout=1500)
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert " passed" in r.stdout and "failed" not in r.stdout, tail
     # the kernels under test were this package's: the drop-in reports the CUDA library
     probe = subprocess.run([sys.executable, "-c",
                             "from kernels.fused_decode_attn import triton_available as t; print(t()[1])"],
-                           capture_output=True, text=True, env=env, cwd=REF, timeout=300)
+                           capture_output=True, text=True, env=env, cwd=dropin, timeout=300)
     assert "tritonkv_b200" in probe.stdout, probe.stdout + probe.stderr

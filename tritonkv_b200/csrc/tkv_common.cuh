@@ -186,6 +186,13 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// a * b + c on f16 pairs, one rounding
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b),
+                      *reinterpret_cast<__half2*>(&c));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
 // Load element `i` of a query row of any supported dtype, rounded to f16 exactly
 // as the reference's `.to(tl.float16)` does, returned as float.
 __device__ __forceinline__ __half load_q_half(const void* q, int dtype, int64_t i) {

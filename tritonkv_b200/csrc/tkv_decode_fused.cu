@@ -403,9 +403,12 @@ struct FusedPolicy {
   // end set to -inf); `left` = tokens from the tile start to the unit end.
   // Per-channel keys: K = code * s[d] + z[d] with one (s, z) row for the whole tile, so
   //     q.k_n = sum_d (q_d s_d) c_{n,d} + sum_d q_d z_d.
-  // The scale goes into the B operand (q' = q * s, formed once per tile in f16), all chunks
-  // share ONE accumulator, and the zero-point term -- the same for every token of the tile --
-  // is one MMA per chunk whose A operand is the z row repeated down the token rows.
+  // The scale goes into the B operand, formed per chunk as an f16 pair hi + lo with
+  // hi = rn(q s) and lo = fma(q, s, -hi), the exact rounding error of hi -- an outlier channel
+  // has a large s, and q s rounded to f16 once would put 2^-11 of the largest terms into
+  // every score.  All chunks share ONE accumulator per 16 tokens, and the zero-point term --
+  // the same for every token of the tile -- is one MMA per chunk whose A operand is the z
+  // row repeated down the token rows.
   __device__ static __forceinline__ void scores_kchan(Scores& out, const Query& qq, uint32_t st,
                                                       int left, float qk_scale, int lane) {
     const int g = lane >> 2, t = lane & 3;
@@ -414,69 +417,69 @@ struct FusedPolicy {
     const uint32_t ks_r = ms + t * 8;                     // dims 16ch + 4t .. 16ch + 4t + 3 of a chunk
     const uint32_t kz_r = ms + C::META_STRIDE + t * 8;
     const float qk24 = qk_scale * 16777216.f;  // the code fields carry 2^-24
-    uint32_t qs[NCH][2];
     float cz[4];
+    float c[MT][4];
+    bool started = false;  // resolved at compile time: the loops below are fully unrolled
 #pragma unroll
-    for (int ch = 0; ch < NCH; ++ch) {
-      const uint2 sv = lds_v2(ks_r + ch * 32);
-      const uint2 zv = lds_v2(kz_r + ch * 32);
-      // k-slots 2t, 2t+1 <-> dims 16ch+4t, 16ch+4t+2; k-slots 2t+8, 2t+9 <-> dims +1, +3
-      const uint32_t s02 = __byte_perm(sv.x, sv.y, 0x5410), s13 = __byte_perm(sv.x, sv.y, 0x7632);
-      uint32_t z02 = __byte_perm(zv.x, zv.y, 0x5410), z13 = __byte_perm(zv.x, zv.y, 0x7632);
-      qs[ch][0] = hmul2_u32(qq.qf[ch][0], s02);
-      qs[ch][1] = hmul2_u32(qq.qf[ch][1], s13);
-      // the query of bit slice p carries 2^(-NBITS p): the zero row of that slice takes it back
-      const int slice = ch / NBLK;
-      if (slice > 0) {
-        const __half2 up2 = __float2half2_rn(pow2i(NBITS * slice));
-        const uint32_t up = *reinterpret_cast<const uint32_t*>(&up2);
-        z02 = hmul2_u32(z02, up);
-        z13 = hmul2_u32(z13, up);
+    for (int bb = 0; bb < NBLK; bb += 2) {
+      uint32_t r[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if constexpr (NBLK >= 2) {
+          ldmatrix_x4(r[mt], kc + qq.off[mt][bb >> 1]);
+        } else {
+          ldmatrix_x2(r[mt][0], r[mt][1], kc + qq.off[mt][0]);
+          r[mt][2] = r[mt][3] = 0;
+        }
       }
-      if (ch == 0) {
-        mma16816_zero(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
-      } else {
-        mma16816(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
+#pragma unroll
+      for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
+        const int blk = bb + jj;
+#pragma unroll
+        for (int pp = 0; pp < P; ++pp) {
+          constexpr uint32_t M0 = C::MASK0;
+          const uint32_t mask = M0 << (NBITS * pp);
+          const int ch = pp * NBLK + blk;
+          // ---- this chunk's B operands: q s as hi + lo, and the z row against q ----
+          const uint2 sv = lds_v2(ks_r + ch * 32);
+          const uint2 zv = lds_v2(kz_r + ch * 32);
+          // k-slots 2t, 2t+1 <-> dims 16ch+4t, 16ch+4t+2; k-slots 2t+8, 2t+9 <-> dims +1, +3
+          const uint32_t s02 = __byte_perm(sv.x, sv.y, 0x5410), s13 = __byte_perm(sv.x, sv.y, 0x7632);
+          uint32_t z02 = __byte_perm(zv.x, zv.y, 0x5410), z13 = __byte_perm(zv.x, zv.y, 0x7632);
+          const uint32_t hi0 = hmul2_u32(qq.qf[ch][0], s02), hi1 = hmul2_u32(qq.qf[ch][1], s13);
+          const uint32_t lo0 = hfma2_u32(qq.qf[ch][0], s02, hi0 ^ 0x80008000u);
+          const uint32_t lo1 = hfma2_u32(qq.qf[ch][1], s13, hi1 ^ 0x80008000u);
+          if (pp > 0) {  // the query of bit slice p carries 2^(-NBITS p): the zero row takes it back
+            const __half2 up2 = __float2half2_rn(pow2i(NBITS * pp));
+            const uint32_t up = *reinterpret_cast<const uint32_t*>(&up2);
+            z02 = hmul2_u32(z02, up);
+            z13 = hmul2_u32(z13, up);
+          }
+          if (!started) {
+            mma16816_zero(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
+          } else {
+            mma16816(cz, z02, z02, z13, z13, qq.qf[ch][0], qq.qf[ch][1]);
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t xl = r[mt][2 * jj], xh = r[mt][2 * jj + 1];
+            const uint32_t a0 = xl & mask, a1 = xh & mask, a2 = (xl >> 8) & mask, a3 = (xh >> 8) & mask;
+            if (!started) {
+              mma16816_zero(c[mt], a0, a1, a2, a3, hi0, hi1);
+            } else {
+              mma16816(c[mt], a0, a1, a2, a3, hi0, hi1);
+            }
+            mma16816(c[mt], a0, a1, a2, a3, lo0, lo1);
+          }
+          started = true;
+        }
       }
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) cz[i] *= qk_scale;
     float (&sc)[MT][4] = out.s;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      float c[4];
-      bool started = false;
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int bb = 0; bb < NBLK; bb += 2) {
-        uint32_t r[4];
-        if constexpr (NBLK >= 2) {
-          ldmatrix_x4(r, kc + qq.off[mt][bb >> 1]);
-        } else {
-          ldmatrix_x2(r[0], r[1], kc + qq.off[mt][0]);
-          r[2] = r[3] = 0;
-        }
-#pragma unroll
-        for (int jj = 0; jj < (NBLK >= 2 ? 2 : 1); ++jj) {
-          const int blk = bb + jj;
-          const uint32_t xl = r[2 * jj], xh = r[2 * jj + 1];
-          const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
-#pragma unroll
-          for (int pp = 0; pp < P; ++pp) {
-            constexpr uint32_t M0 = C::MASK0;
-            const uint32_t mask = M0 << (NBITS * pp);
-            const int ch = pp * NBLK + blk;
-            if (!started) {
-              mma16816_zero(c, xl & mask, xh & mask, xl8 & mask, xh8 & mask, qs[ch][0], qs[ch][1]);
-              started = true;
-            } else {
-              mma16816(c, xl & mask, xh & mask, xl8 & mask, xh8 & mask, qs[ch][0], qs[ch][1]);
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sc[mt][i] = fmaf(c[i], qk24, cz[i]);
-    }
+      for (int i = 0; i < 4; ++i) sc[mt][i] = fmaf(c[mt][i], qk24, cz[i] * qk_scale);
     if (left < kTok) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {

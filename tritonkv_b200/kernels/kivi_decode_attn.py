@@ -110,11 +110,16 @@ def kivi_decode_attention(q: torch.Tensor, cache: KiviCache, sm_scale: float | N
                 acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(), out.data_ptr(), B, HQ, HKV, S_q, D,
                 kc.nbits, VALUE_GROUP, float(sm_scale), num_splits, split_size, nslots, None,
                 _cabi.FLAG_PARTIALS_ONLY | _cabi.FLAG_K_PER_CHANNEL, stream))
+            if R == 0:  # no fp16 tail: the merge of the split partials is the result
+                return combine_splits(acc, maxs, sums, out=out)
             combine_splits(acc, maxs, sums, out=pacc[parts].view(B, HQ, D), out_m=pm[parts].view(B, HQ),
                            out_l=pl[parts].view(B, HQ))
             parts += 1
         if R > 0:
             w16 = ws.setdefault("kivi_res", {})
+            if S_q == 0:  # shorter than one key group: the fp16 kernel alone
+                return fp16_decode_attention(q, cache.k_res, cache.v_res, sm_scale=sm_scale, out=out,
+                                             _workspace=w16)
             fp16_decode_attention(q, cache.k_res, cache.v_res, sm_scale=sm_scale, out=out,
                                   _workspace=w16, _partials_only=True)
             combine_splits(w16["acc"], w16["maxs"], w16["sums"], out=pacc[parts].view(B, HQ, D),
