@@ -238,6 +238,18 @@ def test_argument_errors_match_reference():
         fused_decode_attention(q, kq8, kq8)
     with pytest.raises(RuntimeError, match="no CPU path"):
         fused_decode_attention(q.cpu(), kq, vq)
+    # cache tensors the kernels would reinterpret silently: refused by dtype and by device
+    f32meta = Q.QuantizedTensor(kq.packed, kq.scale.float(), kq.zero.float(), 4, 32, 128)
+    with pytest.raises(TypeError, match="scale must be float16"):
+        fused_decode_attention(q, f32meta, vq)
+    with pytest.raises(TypeError, match="scale must be float16"):
+        Q.dequantize_groupwise(f32meta)
+    badcodes = Q.QuantizedTensor(kq.packed.to(torch.int8), kq.scale, kq.zero, 4, 32, 128)
+    with pytest.raises(TypeError, match="packed must be uint8"):
+        fused_decode_attention(q, kq, badcodes)
+    cpu_meta = Q.QuantizedTensor(vq.packed, vq.scale.cpu(), vq.zero, 4, 32, 128)
+    with pytest.raises(ValueError, match="is on cpu"):
+        fused_decode_attention(q, kq, cpu_meta)
 
 
 # ------------------------------------------------------------------ fp16 control
