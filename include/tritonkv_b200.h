@@ -42,8 +42,7 @@ extern "C" {
 
 /* flags for the two decode entry points */
 #define TKV_FLAG_PARTIALS_ONLY 1 /* always write (acc,m,l), even when nslots == 1 */
-#define TKV_FLAG_COMBINE 2       /* with nslots > 1: the call also produces out -- merged inside the split kernel when
-                                    `tickets` is given and nslots <= 16, else by an enqueued tkv_combine */
+#define TKV_FLAG_COMBINE 2       /* with nslots > 1: enqueue tkv_combine(acc, m, l -> out) after the split kernel */
 #define TKV_FLAG_K_PER_CHANNEL 4 /* tkv_fused_decode: k_scale/k_zero are (B, HKV, S/32, D), see tkv_quantize_keys_per_channel */
 
 /* kernel ids for tkv_kernel_attrs */
@@ -109,20 +108,13 @@ int tkv_decode_plan(int kernel_id, int nbits, int D, int gs, int B, int HQ, int 
  * m, l (B,HQ,nslots) and `out` is untouched (call tkv_combine with NS = nslots next, or
  * pass TKV_FLAG_COMBINE to have it enqueued by the same call).
  * seq_lens (B,) int32 device pointer or null: per-sequence history length S_b <= S (no
- * reference counterpart; null == S).
- * tickets: null, or B*HKV*ceil((HQ/HKV)/8) int32 counters on the device, all zero before the
- * first call.  With TKV_FLAG_COMBINE and 1 < nslots <= 16 the CTA that stores the last partial
- * of a (batch, KV head, head chunk) -- found by an atomic ticket, no CTA waits -- merges that
- * head's slots and writes out itself, so the step is ONE launch (the reference's single-split
- * epilogue writes out directly too, kernels/fused_decode_attn.py:332-339; with several splits
- * it always launches _combine_splits).  The counters are all zero again when the kernel ends;
- * calls that overlap on the GPU must not share them. */
+ * reference counterpart; null == S). */
 int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_packed, const void* k_scale,
                      const void* k_zero, const uint8_t* v_packed, const void* v_scale,
                      const void* v_zero, float* acc, float* m, float* l, float* out, int B,
                      int HQ, int HKV, int S, int D, int nbits, int gs, float sm_scale,
                      int num_splits, int split_size, int nslots, const int32_t* seq_lens,
-                     int32_t* tickets, int flags, void* stream);
+                     int flags, void* stream);
 
 /* _fp16_decode_attn_split + launcher (kernels/fp16_decode_attn.py:47-135, :166-227):
  * the control with the identical split, scheduling, online softmax, GQA grouping and
@@ -130,7 +122,7 @@ int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_packed, const 
 int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const void* v, float* acc,
                     float* m, float* l, float* out, int B, int HQ, int HKV, int S, int D,
                     float sm_scale, int num_splits, int split_size, int nslots,
-                    const int32_t* seq_lens, int32_t* tickets, int flags, void* stream);
+                    const int32_t* seq_lens, int flags, void* stream);
 
 /* _combine_splits (kernels/fused_decode_attn.py:355-395): log-sum-exp merge over NS
  * partials.  out (B, HQ, D).  If out_m and out_l are non-null the merged result is

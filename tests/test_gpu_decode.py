@@ -655,7 +655,7 @@ def test_combine_flag_equals_two_calls_through_the_c_abi():
             q.data_ptr(), _cabi.dtype_code(q), kq.packed.data_ptr(), kq.scale.data_ptr(),
             kq.zero.data_ptr(), vq.packed.data_ptr(), vq.scale.data_ptr(), vq.zero.data_ptr(),
             acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(), B, HQ, HKV, S, D, nbits, gs,
-            1.0 / D ** 0.5, ns, ss, nslots, None, None, flags, stream))
+            1.0 / D ** 0.5, ns, ss, nslots, None, flags, stream))
         if flags == 0:
             assert torch.isnan(out).all()  # partials only: out untouched
             _cabi.check(lib.tkv_combine(acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(),
@@ -664,62 +664,3 @@ def test_combine_flag_equals_two_calls_through_the_c_abi():
     torch.cuda.synchronize()
     assert torch.equal(outs[0], outs[1])
     assert_close(outs[1], oracle_attention(q, kq, vq), "combine flag")
-
-
-@pytest.mark.parametrize("B,HQ,HKV,S,nbits,kw", [
-    (2, 8, 2, 3000, 4, {}),                    # unit-aligned plan, 12 slots per head
-    (64, 32, 8, 512, 4, {}),                   # balanced dense plan: CTAs straddle units, 2-3 slots
-    (8, 32, 8, 4096, 2, {}),                   # 4 slots per head
-    (3, 24, 2, 1000, 4, {"num_splits": 3}),    # explicit splits, GQA 12 (two head chunks)
-    (16, 32, 8, 2500, 4, {"ragged": True}),    # balanced ragged plan, one sequence without tokens
-])
-def test_in_kernel_merge_through_the_c_abi(B, HQ, HKV, S, nbits, kw):
-    """With ticket counters and few slots per head the split kernel merges the partials itself
-    (one launch): same result as split kernel + combine kernel within rounding (the merge
-    order differs), equal to the oracle, identical when repeated, counters back at zero."""
-    from tritonkv_b200 import _cabi
-    from tritonkv_b200.kernels._launch import split_geometry
-
-    D, gs = 128, 32
-    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=B + S)
-    kq, vq = Q.quantize_kv(k, v, nbits, gs)
-    lens = None
-    if kw.get("ragged"):
-        lens = ragged_seq_lens(B, 1, S, seed=4)
-        lens[2] = 0
-    sl = None if lens is None else lens.to(DEV)
-    lib = _cabi.load()
-    _, ns, ss = split_geometry(S, 64, kw.get("num_splits"), B, HKV, None, ragged=lens is not None)
-    nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S, ns, ss,
-                                  lens is not None)
-    assert 1 < nslots <= _cabi.FUSE_MAX_SLOTS, nslots
-    stream = _cabi.stream_ptr(q.device)
-    tickets = torch.zeros(B * HKV * -(-(HQ // HKV) // 8), dtype=torch.int32, device=DEV)
-    outs = []
-    for t in (None, tickets, tickets):
-        acc = torch.empty(B, HQ, nslots, D, device=DEV)
-        m = torch.empty(B, HQ, nslots, device=DEV)
-        l = torch.empty(B, HQ, nslots, device=DEV)
-        out = torch.full((B, HQ, D), float("nan"), device=DEV)
-        _cabi.check(lib.tkv_fused_decode(
-            q.data_ptr(), _cabi.dtype_code(q), kq.packed.data_ptr(), kq.scale.data_ptr(),
-            kq.zero.data_ptr(), vq.packed.data_ptr(), vq.scale.data_ptr(), vq.zero.data_ptr(),
-            acc.data_ptr(), m.data_ptr(), l.data_ptr(), out.data_ptr(), B, HQ, HKV, S, D, nbits, gs,
-            1.0 / D ** 0.5, ns, ss, nslots, _cabi.ptr(sl), _cabi.ptr(t), _cabi.FLAG_COMBINE, stream))
-        torch.cuda.synchronize()
-        outs.append(out)
-    assert int(tickets.abs().sum()) == 0
-    assert torch.equal(outs[1], outs[2])
-    assert (outs[0] - outs[1]).abs().max().item() < 1e-5
-    assert_close(outs[1], oracle_attention(q, kq, vq, seq_lens=lens), f"in-kernel merge {(B, HQ, HKV, S)}")
-    # the Python entry takes this path by itself and keeps its counters in the workspace
-    ws: dict = {}
-    got = fused_decode_attention(q, kq, vq, num_splits=kw.get("num_splits"), seq_lens=sl, _workspace=ws)
-    assert torch.equal(got, outs[1]) and "tickets" in ws and int(ws["tickets"].abs().sum()) == 0
-    # the fp16 control shares the driver and the merge
-    ws16: dict = {}
-    got16 = fp16_decode_attention(q, k, v, num_splits=kw.get("num_splits"), seq_lens=sl, _workspace=ws16)
-    ref16 = O.reference_decode_attention(q.float().cpu().numpy(), k.float().cpu().numpy(),
-                                         v.float().cpu().numpy(),
-                                         seq_lens=None if lens is None else lens.numpy())
-    assert_close(got16, ref16, "fp16 control, in-kernel merge")

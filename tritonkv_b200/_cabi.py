@@ -26,7 +26,6 @@ DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 FLAG_PARTIALS_ONLY = 1
 FLAG_COMBINE = 2
 FLAG_K_PER_CHANNEL = 4
-FUSE_MAX_SLOTS = 16  # kFuseMaxSlots of the kernels: slots per head the split kernel merges itself
 KERNEL_FUSED_SPLIT, KERNEL_FP16_SPLIT = 0, 1
 KERNEL_FUSED_SPLIT_KCHAN = 4
 
@@ -48,10 +47,10 @@ SIGNATURES = {
     "tkv_fused_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                 c_void_p, c_void_p, c_int, c_void_p]),
+                                 c_void_p, c_int, c_void_p]),
     "tkv_fp16_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                c_int, c_void_p, c_void_p, c_int, c_void_p]),
+                                c_int, c_void_p, c_int, c_void_p]),
     "tkv_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_void_p]),
     "tkv_combine_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

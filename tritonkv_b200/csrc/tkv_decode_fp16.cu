@@ -267,12 +267,12 @@ static int fp16_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStre
 extern "C" int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const void* v, float* acc,
                                float* m, float* l, float* out, int B, int HQ, int HKV, int S, int D,
                                float sm_scale, int num_splits, int split_size, int nslots,
-                               const int32_t* seq_lens, int32_t* tickets, int flags, void* stream) {
+                               const int32_t* seq_lens, int flags, void* stream) {
   using namespace tkv;
   TKV_REQUIRE(q && k && v, TKV_ERR_INVALID, "fp16 decode: null input pointer");
   DecodeParams p{};
   int rc = fill_common(p, "fp16 decode", q, q_dtype, acc, m, l, out, B, HQ, HKV, S, sm_scale,
-                       num_splits, split_size, nslots, seq_lens, tickets, flags);
+                       num_splits, split_size, nslots, seq_lens, flags);
   if (rc != TKV_OK) return rc;
   TKV_REQUIRE(aligned16(k) && aligned16(v), TKV_ERR_ALIGN,
               "fp16 decode: k and v pointers must be 16-byte aligned");
@@ -290,7 +290,6 @@ extern "C" int tkv_fp16_decode(const void* q, int q_dtype, const void* k, const 
   if (rc != TKV_OK) return rc;
   if ((flags & TKV_FLAG_COMBINE) && nslots > 1 && !(flags & TKV_FLAG_PARTIALS_ONLY)) {
     TKV_REQUIRE(out, TKV_ERR_INVALID, "fp16 decode: TKV_FLAG_COMBINE needs out");
-    if (p.tickets != nullptr) return TKV_OK;  // merged inside the split kernel
     return tkv_combine(acc, m, l, out, nullptr, nullptr, B, HQ, nslots, D, stream);
   }
   return TKV_OK;

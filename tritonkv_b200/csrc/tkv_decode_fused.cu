@@ -906,14 +906,13 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
                                 const void* v_scale, const void* v_zero, float* acc, float* m,
                                 float* l, float* out, int B, int HQ, int HKV, int S, int D,
                                 int nbits, int gs, float sm_scale, int num_splits, int split_size,
-                                int nslots, const int32_t* seq_lens, int32_t* tickets, int flags,
-                                void* stream) {
+                                int nslots, const int32_t* seq_lens, int flags, void* stream) {
   using namespace tkv;
   TKV_REQUIRE(q && k_packed && k_scale && k_zero && v_packed && v_scale && v_zero, TKV_ERR_INVALID,
               "fused decode: null input pointer");
   DecodeParams p{};
   int rc = fill_common(p, "fused decode", q, q_dtype, acc, m, l, out, B, HQ, HKV, S, sm_scale,
-                       num_splits, split_size, nslots, seq_lens, tickets, flags);
+                       num_splits, split_size, nslots, seq_lens, flags);
   if (rc != TKV_OK) return rc;
   TKV_REQUIRE(aligned16(k_packed) && aligned16(v_packed), TKV_ERR_ALIGN,
               "fused decode: packed code pointers must be 16-byte aligned");
@@ -967,7 +966,6 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
   if (rc != TKV_OK) return rc;
   if ((flags & TKV_FLAG_COMBINE) && nslots > 1 && !(flags & TKV_FLAG_PARTIALS_ONLY)) {
     TKV_REQUIRE(out, TKV_ERR_INVALID, "fused decode: TKV_FLAG_COMBINE needs out");
-    if (p.tickets != nullptr) return TKV_OK;  // merged inside the split kernel
     return tkv_combine(acc, m, l, out, nullptr, nullptr, B, HQ, nslots, D, stream);
   }
   return TKV_OK;

@@ -16,12 +16,6 @@ namespace {
 constexpr size_t kScratchFloats = size_t(2) << 20;
 static __device__ __align__(256) float g_decode_scratch[kScratchFloats];
 
-// Ticket counters of the in-kernel merge (one per sequence x KV head x chunk of 8 query heads),
-// zero at load and left zero by every kernel that uses them.  With them the call runs the same
-// kernels as tkv_fused_decode does for a caller that passes tickets, so both give the same bits.
-constexpr int kStaticTickets = 16384;
-static __device__ __align__(256) int g_decode_tickets[kStaticTickets];
-
 // In host code the array's name is only a handle for the runtime, not a device address,
 // so the address is asked for once per device (with that device current) and cached.
 // Concurrent first calls may both do the look-up and store the same value.  The cache
@@ -29,22 +23,18 @@ static __device__ __align__(256) int g_decode_tickets[kStaticTickets];
 // entry point on that device afterwards.
 constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {};
-int* g_tickets_ptr[kMaxDevices] = {};
 
-int scratch_for_current_device(float** out, int** tickets) {
+int scratch_for_current_device(float** out) {
   int dev = 0;
   TKV_CUDA(cudaGetDevice(&dev));
   TKV_REQUIRE(dev >= 0 && dev < kMaxDevices, TKV_ERR_INVALID,
               "fused_decode_static: device index %d out of range", dev);
-  if (g_scratch_ptr[dev] == nullptr || g_tickets_ptr[dev] == nullptr) {
+  if (g_scratch_ptr[dev] == nullptr) {
     void* p = nullptr;
-    TKV_CUDA(cudaGetSymbolAddress(&p, g_decode_tickets));
-    g_tickets_ptr[dev] = static_cast<int*>(p);
     TKV_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
     g_scratch_ptr[dev] = static_cast<float*>(p);
   }
   *out = g_scratch_ptr[dev];
-  *tickets = g_tickets_ptr[dev];
   return TKV_OK;
 }
 
@@ -69,13 +59,12 @@ extern "C" int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t
   // The one-time look-up of the scratch address happens on the first call on a device,
   // whatever the plan of that call, so that a warm-up call always completes the set-up.
   float* base = nullptr;
-  int* tickets = nullptr;
-  rc = scratch_for_current_device(&base, &tickets);
+  rc = scratch_for_current_device(&base);
   if (rc != TKV_OK) return rc;
   if (nslots == 1)  // nothing to merge: the scratch is not touched
     return tkv_fused_decode(q, q_dtype, k_packed, k_scale, k_zero, v_packed, v_scale, v_zero,
                             nullptr, nullptr, nullptr, out, B, HQ, HKV, S, D, nbits, gs, sm_scale,
-                            1, split_size, 1, nullptr, nullptr, 0, stream);
+                            1, split_size, 1, nullptr, 0, stream);
   const size_t rows = (size_t)B * HQ * nslots;
   const size_t need = rows * ((size_t)D + 2);
   TKV_REQUIRE(need <= kScratchFloats, TKV_ERR_UNSUPPORTED,
@@ -87,10 +76,9 @@ extern "C" int tkv_fused_decode_static(const void* q, int q_dtype, const uint8_t
   float* l = m + rows;
   // Every slot the combine reads is written by the split kernel in this call (data slots
   // and the m = -inf markers of unused ones), so nothing has to be cleared between calls.
-  // With few slots per head the split kernel merges them itself (as it does for callers of
-  // tkv_fused_decode that pass tickets); otherwise the combine kernel is enqueued behind it.
-  const int64_t heads = (int64_t)B * HKV * (((HQ / HKV) + 7) / 8);
-  return tkv_fused_decode(q, q_dtype, k_packed, k_scale, k_zero, v_packed, v_scale, v_zero, acc, m, l,
-                          out, B, HQ, HKV, S, D, nbits, gs, sm_scale, 1, split_size, nslots, nullptr,
-                          heads <= kStaticTickets ? tickets : nullptr, TKV_FLAG_COMBINE, stream);
+  rc = tkv_fused_decode(q, q_dtype, k_packed, k_scale, k_zero, v_packed, v_scale, v_zero, acc, m, l,
+                        out, B, HQ, HKV, S, D, nbits, gs, sm_scale, 1, split_size, nslots, nullptr,
+                        0, stream);
+  if (rc != TKV_OK) return rc;
+  return tkv_combine(acc, m, l, out, nullptr, nullptr, B, HQ, nslots, D, stream);
 }

@@ -26,7 +26,6 @@ struct DecodeParams {
   float* l;
   float* out;
   const int32_t* seq_lens;
-  int32_t* tickets;  // one counter per (batch, KV head, head chunk), all zero between launches; or null
   int B, HQ, HKV, S;
   int group;       // HQ / HKV
   int hchunks;     // ceil(group / 8): CTAs per KV head along the head axis

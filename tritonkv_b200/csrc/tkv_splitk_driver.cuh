@@ -212,45 +212,6 @@ struct IssueCursor {
   int g_end;      // end of the cursor's segment
 };
 
-// In-kernel merge.  With few partial slots per head the CTA that stores the LAST partial of a
-// (batch, KV head, head chunk) -- found by an atomic ticket, nobody waits -- merges all slots
-// of its eight heads and writes the normalised output itself, so the step needs no second
-// kernel.  The arithmetic is the small combine kernel's (slots in order, fused multiply-adds).
-constexpr int kFuseMaxSlots = 16;
-
-template <int D, int THREADS>
-__device__ __forceinline__ void merge_head_slots(const DecodeParams& p, int nslots, int b, int hkv,
-                                                 int hc) {
-  constexpr int D4 = D / 4;
-  for (int idx = threadIdx.x; idx < kHeadsPerCta * D4; idx += THREADS) {
-    const int h = idx / D4, d = (idx - h * D4) * 4;
-    const int hg = hc * kHeadsPerCta + h;
-    if (hg >= p.group) continue;
-    const int64_t hq = (int64_t)b * p.HQ + hkv * p.group + hg;
-    const float* mrow = p.m + hq * nslots;
-    const float* lrow = p.l + hq * nslots;
-    const float* arow = p.acc + hq * nslots * D + d;
-    float M = -INFINITY;
-    for (int s = 0; s < nslots; ++s) M = fmaxf(M, __ldcg(mrow + s));
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    float L = 0.f;
-    for (int s = 0; s < nslots; ++s) {
-      const float ms = __ldcg(mrow + s);
-      const float w = (ms > -INFINITY) ? ex2(ms - M) : 0.f;
-      if (w > 0.f) {  // empty slots may hold anything in acc: never use it
-        const float4 x = __ldcg(reinterpret_cast<const float4*>(arow + (int64_t)s * D));
-        a.x = fmaf(w, x.x, a.x);
-        a.y = fmaf(w, x.y, a.y);
-        a.z = fmaf(w, x.z, a.z);
-        a.w = fmaf(w, x.w, a.w);
-        L = fmaf(w, __ldcg(lrow + s), L);
-      }
-    }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    *reinterpret_cast<float4*>(p.out + hq * D + d) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
-  }
-}
-
 // MODE: 1 = balanced ranges over the dense tile sequence, 3 = the same over a ragged batch,
 // 2 = one segment per CTA (unit-aligned plans and the static plan).  A compile-time mode
 // keeps the single-segment kernel -- the latency-critical one, small batches -- free of the
@@ -275,7 +236,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   __shared__ float s_m[WARPS][kHeadsPerCta];
   __shared__ float s_l[WARPS][kHeadsPerCta];
   __shared__ int s_slot[WARPS];
-  __shared__ int s_last;  // in-kernel merge: this CTA stored the last partial of its heads
 
   // the shuffle tells the compiler that the warp index is warp-uniform, so the ring, cursor and
   // barrier arithmetic that hangs off it can go to the uniform datapath
@@ -329,41 +289,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   int g0, g1;
   int TC = sc.TC;  // tiles per CTA (computed here for ragged batches)
   Segment seg;
-  // In-kernel merge: every CTA that owns a slot of (b, hkv, hc) calls this after its stores;
-  // the one that draws the last ticket merges the head's slots and resets the counter.
-  auto arrive_and_merge = [&](int b, int hkv, int hc) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int hk = hkv * p.hchunks + hc;
-      int expected;
-      if constexpr (MODE == 2) {
-        expected = sc.persistent == 2 ? sc.NS * sc.SEG : sc.NS;
-      } else {
-        expected = 0;
-        for (int sp = 0; sp < sc.NS; ++sp) {
-          int u0, tu;
-          if constexpr (MODE == 3) {
-            tu = s_pref[b + 1] - s_pref[b];
-            u0 = sc.HKVc * s_pref[b] + hk * tu;
-          } else {
-            tu = (sp == sc.NS - 1) ? sc.TUl : sc.TUf;
-            u0 = (b * sc.HKVc + hk) * sc.T_seq + sp * sc.TUf;
-          }
-          expected += (u0 + tu - 1) / TC - u0 / TC + 1;
-        }
-      }
-      int* t = p.tickets + ((int64_t)b * p.HKV * p.hchunks + hk);
-      const int drawn = atomicAdd(t, 1);
-      s_last = drawn == expected - 1;
-      if (s_last) *t = 0;  // every owner has arrived: the counter is clean for the next launch
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      merge_head_slots<D, WARPS * 32>(p, sc.nslots, b, hkv, hc);
-    }
-  };
   constexpr bool kMulti = (MODE & 1) != 0;  // a CTA may serve several segments
   auto seg_at = [&](int g, int g_hi) {
     if constexpr (MODE == 3) {
@@ -407,7 +332,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     // units without tokens are touched by no range: their slots are marked empty here
     for (int u = cta; u < p.B * sc.HKVc; u += gridDim.x) {
       const int b = u / sc.HKVc, hk = u - b * sc.HKVc;
-      if (s_pref[b + 1] == s_pref[b] && p.partials && p.tickets == nullptr) {
+      if (s_pref[b + 1] == s_pref[b] && p.partials) {
         const int hkv = hk / p.hchunks, hc = hk - hkv * p.hchunks;
         for (int idx = threadIdx.x; idx < kHeadsPerCta * sc.SEG; idx += WARPS * 32) {
           const int h = idx / sc.SEG, j = idx - h * sc.SEG;
@@ -462,7 +387,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
           p.l[hq * sc.nslots + seg.slot] = 0.f;
         }
       }
-      if (p.tickets != nullptr) arrive_and_merge(seg.b, seg.hkv, seg.hc);
       return;
     }
   } else {
@@ -728,7 +652,6 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
         }
       }
     }
-    if (p.tickets != nullptr) arrive_and_merge(seg.b, seg.hkv, seg.hc);
     __syncthreads();
     need_proxy_fence = true;
     if (!Policy::PIPELINED && deferred_issue) issue_next();
@@ -940,7 +863,7 @@ struct SplitLaunch {
 inline int fill_common(DecodeParams& p, const char* who, const void* q, int q_dtype, float* acc,
                        float* m, float* l, float* out, int B, int HQ, int HKV, int S,
                        float sm_scale, int num_splits, int split_size, int nslots,
-                       const int32_t* seq_lens, int32_t* tickets, int flags) {
+                       const int32_t* seq_lens, int flags) {
   TKV_REQUIRE(B > 0 && HQ > 0 && HKV > 0 && S > 0, TKV_ERR_INVALID,
               "%s: B, HQ, HKV, S must be positive (got %d, %d, %d, %d)", who, B, HQ, HKV, S);
   TKV_REQUIRE((int64_t)B * HKV * S < (1LL << 31), TKV_ERR_INVALID,
@@ -968,11 +891,6 @@ inline int fill_common(DecodeParams& p, const char* who, const void* q, int q_dt
   p.l = l;
   p.out = out;
   p.seq_lens = seq_lens;
-  // the in-kernel merge serves a combining call whose plan has few slots per head
-  p.tickets = ((flags & TKV_FLAG_COMBINE) && !(flags & TKV_FLAG_PARTIALS_ONLY) && nslots > 1 &&
-               nslots <= kFuseMaxSlots)
-                  ? tickets
-                  : nullptr;
   p.B = B;
   p.HQ = HQ;
   p.HKV = HKV;

@@ -118,19 +118,6 @@ def get_workspace(ws: dict, B: int, HQ: int, nslots: int, D: int, device, force_
     return acc, maxs, sums
 
 
-def get_tickets(ws: dict, n: int, device) -> torch.Tensor:
-    """``n`` zeroed int32 counters kept in the caller's workspace dict (key ``tickets``): one
-    per (sequence, KV head, chunk of 8 query heads).  The split kernel uses them to find the
-    CTA that stores a head's last partial, which then merges the head's slots itself; it
-    leaves them zero, so they are allocated and cleared once.  No reference counterpart (its
-    launcher always runs ``_combine_splits`` as a second kernel, :558-568)."""
-    t = ws.get("tickets")
-    if t is None or t.numel() < n or t.device != device:
-        t = torch.zeros(max(n, 64), device=device, dtype=torch.int32)
-        ws["tickets"] = t
-    return t
-
-
 def check_out(out, B: int, HQ: int, D: int, device):
     if out is None:
         return torch.empty((B, HQ, D), device=device, dtype=torch.float32)

@@ -15,8 +15,7 @@ import math
 import torch
 
 from .. import _cabi
-from ._launch import (check_out, check_seq_lens, get_tickets, get_workspace, q_for_kernel,
-                      split_geometry)
+from ._launch import (check_out, check_seq_lens, get_workspace, q_for_kernel, split_geometry)
 
 
 def fp16_decode_attention(
@@ -72,9 +71,6 @@ def fp16_decode_attention(
         out = check_out(out, B, HQ, D, device)
         ws = _workspace if _workspace is not None else {}
         acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
-        tickets = None
-        if not _partials_only and 1 < nslots <= _cabi.FUSE_MAX_SLOTS:
-            tickets = get_tickets(ws, B * HKV * -(-(HQ // HKV) // 8), device)
 
         stream = _cabi.stream_ptr(device)
         # one call enqueues the split kernel and, when there are partials to merge, the combine
@@ -83,5 +79,5 @@ def fp16_decode_attention(
             q.data_ptr(), _cabi.dtype_code(q), k.data_ptr(), v.data_ptr(),
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
             B, HQ, HKV, S, D, float(sm_scale), num_splits, split_size, nslots,
-            _cabi.ptr(seq_lens), _cabi.ptr(tickets), flags, stream))
+            _cabi.ptr(seq_lens), flags, stream))
     return out

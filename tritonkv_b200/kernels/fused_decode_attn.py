@@ -18,8 +18,8 @@ import torch
 
 from .. import _cabi
 from ..quantize import QuantizedTensor, check_cache_tensors
-from ._launch import (check_out, check_seq_lens, combine_splits, get_tickets, get_workspace,
-                      pick_num_splits, q_for_kernel, split_geometry)
+from ._launch import (check_out, check_seq_lens, combine_splits, get_workspace, pick_num_splits,
+                      q_for_kernel, split_geometry)
 
 __all__ = ["fused_decode_attention", "triton_available", "pick_num_splits", "combine_splits"]
 
@@ -130,10 +130,6 @@ def fused_decode_attention(
             out = check_out(out, B, HQ, D, device)
         ws = _workspace if _workspace is not None else {}
         acc, maxs, sums = get_workspace(ws, B, HQ, nslots, D, device, _partials_only)
-        # few slots per head: the split kernel merges them itself (one launch per step)
-        tickets = None
-        if not _partials_only and 1 < nslots <= _cabi.FUSE_MAX_SLOTS:
-            tickets = get_tickets(ws, B * HKV * -(-(HQ // HKV) // 8), device)
 
         stream = _cabi.stream_ptr(device)
         # one call enqueues the split kernel and, when there are partials to merge, the combine
@@ -144,5 +140,5 @@ def fused_decode_attention(
             vp.data_ptr(), vs.data_ptr(), vz.data_ptr(),
             _cabi.ptr(acc), _cabi.ptr(maxs), _cabi.ptr(sums), out.data_ptr(),
             B, HQ, HKV, S, D, nbits, gs, float(sm_scale), num_splits, split_size, nslots,
-            _cabi.ptr(seq_lens), _cabi.ptr(tickets), flags, stream))
+            _cabi.ptr(seq_lens), flags, stream))
     return out

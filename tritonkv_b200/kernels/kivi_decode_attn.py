@@ -108,7 +108,7 @@ def kivi_decode_attention(q: torch.Tensor, cache: KiviCache, sm_scale: float | N
                 q.data_ptr(), _cabi.dtype_code(q), kc.packed.data_ptr(), kc.scale.data_ptr(),
                 kc.zero.data_ptr(), vq.packed.data_ptr(), vq.scale.data_ptr(), vq.zero.data_ptr(),
                 acc.data_ptr(), maxs.data_ptr(), sums.data_ptr(), out.data_ptr(), B, HQ, HKV, S_q, D,
-                kc.nbits, VALUE_GROUP, float(sm_scale), num_splits, split_size, nslots, None, None,
+                kc.nbits, VALUE_GROUP, float(sm_scale), num_splits, split_size, nslots, None,
                 _cabi.FLAG_PARTIALS_ONLY | _cabi.FLAG_K_PER_CHANNEL, stream))
             if R == 0:  # no fp16 tail: the merge of the split partials is the result
                 return combine_splits(acc, maxs, sums, out=out)
