@@ -641,7 +641,7 @@ def test_combine_flag_equals_two_calls_through_the_c_abi():
     q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=31)
     kq, vq = Q.quantize_kv(k, v, nbits, gs)
     lib = _cabi.load()
-    _, ns, ss = split_geometry(S, 64, None, B, HKV, None)
+    _, ns, ss = split_geometry(S, 64, 4, B, HKV, None)  # explicit splits: several partial slots per head
     nslots, _ = _cabi.decode_plan(_cabi.KERNEL_FUSED_SPLIT, nbits, D, gs, B, HQ, HKV, S, ns, ss, False)
     assert nslots > 1
     stream = _cabi.stream_ptr(q.device)
