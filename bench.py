@@ -523,6 +523,38 @@ def per_channel_cell(cx, name, B, S, seed, b_lo, world):
             "what": "split kernel on per-channel keys + merge of its partials (no fp16 tail at this length)"}
 
 
+def write_side_record(cx, name, B, S, nbits):
+    """The cache's write side on the workload's shape: (a) quantise + pack the whole K tensor
+    into a preallocated cache (what a prefill does; ``quantize.append_groupwise`` with all S
+    tokens: the one-launch quantiser writing in place, no allocation), timed cold by size
+    (the fp16 input alone is several times L2), against its algorithmic bytes
+    ``2*D + D*nbits/8 + 4*D/gs`` per token row; (b) the decode loop's append of one new token
+    per sequence to K and V (two launches)."""
+    torch = cx.torch
+    from tritonkv_b200 import quantize as Q
+
+    _, HQ, HKV, D = WORKLOADS[name][:4]
+    g = torch.Generator(device=cx.device).manual_seed(7)
+    x = torch.randn(B, HKV, S, D, generator=g, device=cx.device, dtype=torch.float32).half()
+    cache = Q.empty_cache(B, HKV, S, D, nbits, GS, cx.device)
+    fns = [lambda: Q.append_groupwise(cache, x, 0)]
+    st = cx.time_steps(fns, K=10, W=3, graphs=False)
+    rows = B * HKV * S
+    byt = rows * (2 * D + D * nbits // 8 + 4 * D // GS)
+    t_us = us(st, 10)
+    rec = {"quantize_pack_us": t_us, "tokens_rows": rows, "bytes": byt,
+           "GBps": byt / (t_us * 1e-6) / 1e9, "frac_of_peak": byt / (t_us * 1e-6) / 1e9 / cx.peak,
+           "what": f"fp16 (B,HKV,S,D) -> {nbits}-bit packed cache in place, one launch"}
+    del x
+    kq, vq = cache, Q.empty_cache(B, HKV, S, D, nbits, GS, cx.device)
+    kn = torch.randn(B, HKV, 1, D, device=cx.device, dtype=torch.float16)
+    vn = torch.randn_like(kn)
+    pos = torch.full((B,), S // 2, device=cx.device, dtype=torch.int32)
+    st = cx.time_steps([lambda: Q.append_kv(kq, vq, kn, vn, pos)])
+    rec["append_one_token_us"] = us(st, cx.K)
+    return rec
+
+
 def us(stats, K):
     return stats["median_ms"] * 1e3 / K
 
@@ -751,6 +783,9 @@ def run_ours(args):
             extras["two_bit"] = two
             del c2
             extras["per_channel_keys_2bit"] = per_channel_cell(cx, name, B_loc, S_loc, seed, b_lo, world)
+            if rank == 0 and world == 1:
+                torch.cuda.empty_cache()
+                extras["write_side"] = write_side_record(cx, name, B_loc, S_loc, nbits)
         torch.cuda.empty_cache()
     cx.barrier()
 

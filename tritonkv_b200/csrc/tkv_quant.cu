@@ -6,46 +6,65 @@
 // every float operation below is a single IEEE round-to-nearest operation written
 // with an explicit intrinsic so that neither FMA contraction nor a fast-math flag
 // can change it.
+#include <type_traits>
+
 #include "tkv_common.cuh"
 
 namespace tkv {
 
 // ---------------------------------------------------------------- quantize + pack
-// Each thread owns 8 consecutive elements of a row.  A quantisation group spans
-// GS/8 adjacent lanes; min/max are butterfly-reduced inside it.  The 8 codes of a
-// thread form a 64-bit word (one code per byte); split-P packing ORs the words of
-// the P lanes that hold dims j, j+DP, ... shifted by their bit-slice position.
-template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&x)[8]);
+// Each thread owns E consecutive elements of a row (E = 16 for f16/bf16 rows: two 16-byte loads;
+// E = 8 otherwise), in kRowsPerThread rows.  A quantisation group spans GS/E adjacent lanes; min
+// and max are butterfly-reduced inside it as the pair (min, -max) with a NaN-propagating
+// minimum -- for 16-bit inputs as ONE packed half2 per shuffle.  The codes of a thread are E/4
+// 32-bit words (one code per byte); split-P packing ORs the words of the P lanes that hold
+// dims j, j+DP, ... shifted by their bit-slice position.  Every size is a power of two, so all
+// index arithmetic is shifts.
+//
+// Codes.  The reference computes round((x - zero) / scale) with an IEEE division.  Here the
+// quotient is a * (1/scale): within 1e-5 of the IEEE quotient wherever the clamp does not
+// decide the code (|q| <= 17), so it rounds to the same integer unless it lies within 1e-4 of
+// a half-integer -- those elements (about one in 1500 for f16 data, whose quotients hit exact
+// ties) are redone with the IEEE division.  Bit-exact, at a fifth of the instructions.
+// The scale's division by 2^nbits - 1 is q0 = d*R, q1 = fma(fma(-q0, QMAX, d), R, q0) with R the
+// rounded reciprocal: the correctly rounded quotient for every finite d (checked against the
+// IEEE division over 160 M values of d, all fp16 values among them).
+constexpr int kRowsPerThread = 2;
 
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* p, float (&x)[8]) {
-  const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(h[i]);
-    x[2 * i] = f.x;
-    x[2 * i + 1] = f.y;
-  }
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float d;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
 }
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[8]) {
-  const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(h[i]);
-    x[2 * i] = f.x;
-    x[2 * i + 1] = f.y;
-  }
+__device__ __forceinline__ float rcp_approx(float a) {
+  float d;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(a));
+  return d;
 }
+
+// A thread's E elements as f32 plus their (min, -max); NaN propagates to both (torch's
+// amin/amax do; fminf/fmaxf would drop it).  For 16-bit types the pair stays a packed half2.
+template <typename T>
+struct Pair16;
 template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&x)[8]) {
-  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-  x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+struct Pair16<__half> { using type = __half2; };
+template <>
+struct Pair16<__nv_bfloat16> { using type = __nv_bfloat162; };
+
+template <typename H2>
+__device__ __forceinline__ float2 widen2(H2 h);
+template <>
+__device__ __forceinline__ float2 widen2<__half2>(__half2 h) { return __half22float2(h); }
+template <>
+__device__ __forceinline__ float2 widen2<__nv_bfloat162>(__nv_bfloat162 h) { return __bfloat1622float2(h); }
+
+// (min over both halves of a, -max over both halves of b) as one packed pair
+template <typename H2>
+__device__ __forceinline__ H2 fold_minmax(H2 a, H2 b) {
+  b = __hneg2(b);
+  const uint32_t au = *reinterpret_cast<const uint32_t*>(&a), bu = *reinterpret_cast<const uint32_t*>(&b);
+  const uint32_t lo = __byte_perm(au, bu, 0x5410), hi = __byte_perm(au, bu, 0x7632);  // (a.x, b.x), (a.y, b.y)
+  return __hmin2_nan(*reinterpret_cast<const H2*>(&lo), *reinterpret_cast<const H2*>(&hi));
 }
 
 // Where the rows go when new tokens are appended to a preallocated cache (cap == 0: in place).
@@ -57,79 +76,155 @@ struct AppendMap {
   int64_t cap;         // token rows per (sequence, head) in the cache
 };
 
-template <typename T, int NBITS>
+// `tpr_shift` = log2(D/E) (threads per row), `lpg_shift` = log2(GS/E) (lanes per group).  Block
+// b handles rows [b*RPB, (b+1)*RPB) with RPB = kRowsPerThread * 256 / tpr, thread t the column
+// block t % tpr of rows b*RPB + t/tpr + i*(256/tpr).
+template <typename T, int NBITS, int E>
 __global__ void __launch_bounds__(256)
     quantize_pack_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed,
                          __half* __restrict__ scale, __half* __restrict__ zero, int64_t rows,
-                         int D, int gs, const AppendMap am) {
-  constexpr int P = 8 / NBITS;
+                         int tpr_shift, int lpg_shift, const AppendMap am) {
+  constexpr int P = 8 / NBITS, LOG2P = NBITS == 4 ? 1 : 2;
   constexpr float QMAX = float((1 << NBITS) - 1);
-  const int tpr = D >> 3;                 // threads per row
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t row = tid / tpr;
-  const int c = (int)(tid % tpr);         // 8-element column block
-  const bool live = row < rows;
-  // Lanes past the end mirror the last row so the shuffles below stay full-warp.
-  const int64_t r = live ? row : rows - 1;
-
-  float v[8];
-  load8<T>(x + r * D + 8 * c, v);
-  float mn = v[0], mx = v[0];
-  bool has_nan = v[0] != v[0];
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: x + kMagic holds rint(x) in its low mantissa bits
+  constexpr bool k16 = !std::is_same<T, float>::value;
+  static_assert(E == 8 || (E == 16 && k16), "16 elements per thread are two 16-byte loads of a 16-bit type");
+  const int tpr = 1 << tpr_shift;
+  const int c = threadIdx.x & (tpr - 1);            // E-element column block
+  const int rstep = 256 >> tpr_shift;               // rows of one pass of the block
+  const int64_t row0 = (int64_t)blockIdx.x * (kRowsPerThread * rstep) + (threadIdx.x >> tpr_shift);
+  const int lanes_per_group = 1 << lpg_shift;
+  const int tps_shift = tpr_shift - LOG2P;          // lanes per bit slice
+  const int p = c >> tps_shift;
+  const int D = E << tpr_shift;
 #pragma unroll
-  for (int i = 1; i < 8; ++i) {
-    mn = fminf(mn, v[i]);
-    mx = fmaxf(mx, v[i]);
-    has_nan |= v[i] != v[i];
-  }
-  const int lanes_per_group = gs >> 3;
-  for (int off = 1; off < lanes_per_group; off <<= 1) {
-    mn = fminf(mn, __shfl_xor_sync(kFullMask, mn, off));
-    mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, off));
-    has_nan |= __shfl_xor_sync(kFullMask, (int)has_nan, off) != 0;
-  }
-  // torch's amin/amax propagate NaN where fminf/fmaxf drop it: a group that holds a NaN
-  // gets zero = NaN, scale = 1 and all codes 0, as the reference produces.
-  if (has_nan) mn = mx = __int_as_float(0x7fc00000);
-  float sc = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
-  sc = (sc > 0.f) ? sc : 1.f;
-  const __half sc16 = __float2half_rn(sc);
-  const __half ze16 = __float2half_rn(mn);
-  const float scf = __half2float(sc16), zef = __half2float(ze16);
-
-  uint64_t word = 0;
+  for (int it = 0; it < kRowsPerThread; ++it) {
+    const int64_t row = row0 + it * rstep;
+    const bool live = row < rows;
+    // Lanes past the end mirror the last row so the shuffles below stay full-warp.
+    const int64_t r = live ? row : rows - 1;
+    const T* src = x + r * D + E * c;
+    float v[E], mn, nmx;
+    if constexpr (k16) {
+      using H2 = typename Pair16<T>::type;
+      H2 h[E / 2];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float t = rintf(__fdiv_rn(__fsub_rn(v[i], zef), scf));
-    t = fminf(fmaxf(t, 0.f), QMAX);
-    word |= (uint64_t)(uint32_t)(int)t << (8 * i);
-  }
-  // split-P: lane c = p*TPS + c' contributes bit slice p of bytes [8c', 8c'+8)
-  const int tps = tpr / P;
-  const int p = c / tps;
-  word <<= (NBITS * p);
-  for (int off = tps; off < tpr; off <<= 1) {
-    const uint32_t lo = __shfl_xor_sync(kFullMask, (uint32_t)word, off);
-    const uint32_t hi = __shfl_xor_sync(kFullMask, (uint32_t)(word >> 32), off);
-    word |= ((uint64_t)hi << 32) | lo;
-  }
-  // Output row: the input row itself, or (append) slot pos[b] + t of sequence (b, head)
-  // in a cache of `cap` token rows per sequence; tokens that fall outside are dropped.
-  int64_t orow = row;
-  bool keep = live;
-  if (am.cap > 0 && live) {
-    const int64_t bh = row / am.t_new;
-    const int t = (int)(row - bh * am.t_new);
-    const int64_t at = (am.pos ? (int64_t)am.pos[bh / am.hkv] : (int64_t)am.pos0) + t;
-    keep = at >= 0 && at < am.cap;
-    orow = bh * am.cap + at;
-  }
-  if (keep) {
-    if (p == 0) *reinterpret_cast<uint64_t*>(packed + orow * (D / P) + 8 * c) = word;
-    if ((c % lanes_per_group) == 0) {
-      const int64_t gi = orow * (D / gs) + (8 * c) / gs;
-      scale[gi] = sc16;
-      zero[gi] = ze16;
+      for (int i = 0; i < E / 8; ++i)
+        *reinterpret_cast<uint4*>(&h[4 * i]) = __ldg(reinterpret_cast<const uint4*>(src) + i);
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) {
+        const float2 f = widen2<H2>(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+      H2 lo = h[0], hi = h[0];
+#pragma unroll
+      for (int i = 1; i < E / 2; ++i) {
+        lo = __hmin2_nan(lo, h[i]);
+        hi = __hmax2_nan(hi, h[i]);
+      }
+      H2 pm = fold_minmax<H2>(lo, hi);
+      for (int off = 1; off < lanes_per_group; off <<= 1) {
+        const uint32_t o = __shfl_xor_sync(kFullMask, *reinterpret_cast<const uint32_t*>(&pm), off);
+        pm = __hmin2_nan(pm, *reinterpret_cast<const H2*>(&o));
+      }
+      const float2 f = widen2<H2>(pm);
+      mn = f.x;
+      nmx = f.y;
+    } else {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      mn = v[0];
+      nmx = -v[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) {
+        mn = min_nan(mn, v[i]);
+        nmx = min_nan(nmx, -v[i]);
+      }
+      for (int off = 1; off < lanes_per_group; off <<= 1) {
+        mn = min_nan(mn, __shfl_xor_sync(kFullMask, mn, off));
+        nmx = min_nan(nmx, __shfl_xor_sync(kFullMask, nmx, off));
+      }
+    }
+    // A group that holds a NaN gets zero = NaN, scale = 1 and all codes 0, as the reference produces.
+    const float range = __fsub_rn(-nmx, mn);
+    const float q0 = __fmul_rn(range, 1.f / QMAX);
+    const float q1 = __fmaf_rn(__fmaf_rn(-q0, QMAX, range), 1.f / QMAX, q0);
+    float sc = range == INFINITY ? range : q1;  // = __fdiv_rn(range, QMAX)
+    sc = (sc > 0.f) ? sc : 1.f;
+    const __half sc16 = __float2half_rn(sc);
+    const __half ze16 = __float2half_rn(mn);
+    const float scf = __half2float(sc16), zef = __half2float(ze16);
+    const float rs = __fmul_rn(rcp_approx(scf), 1.f / QMAX);  // a * rs = quotient / QMAX, saturated to [0, 1]
+
+    float m[E];
+    bool near_tie = false;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float u = __saturatef(__fmul_rn(__fsub_rn(v[i], zef), rs));  // NaN -> 0, as the clamp gives
+      m[i] = __fmaf_rn(u, QMAX, kMagic);
+      const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));      // distance to the integer taken
+      near_tie |= fabsf(d) > 0.4999f;
+    }
+    if (near_tie) {  // a minority of the warps comes here, for one element or two
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const float u = __saturatef(__fmul_rn(__fsub_rn(v[i], zef), rs));
+        const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));
+        if (fabsf(d) > 0.4999f) {
+          float t = rintf(__fdiv_rn(__fsub_rn(v[i], zef), scf));
+          t = fminf(fmaxf(t, 0.f), QMAX);
+          m[i] = __fadd_rn(t, kMagic);
+        }
+      }
+    }
+    uint32_t w[E / 4];  // codes, one per byte
+#pragma unroll
+    for (int i = 0; i < E / 4; ++i) {
+      const uint32_t a = __byte_perm(__float_as_uint(m[4 * i]), __float_as_uint(m[4 * i + 1]), 0x0040);
+      const uint32_t b = __byte_perm(__float_as_uint(m[4 * i + 2]), __float_as_uint(m[4 * i + 3]), 0x0040);
+      w[i] = __byte_perm(a, b, 0x5410) << (NBITS * p);
+    }
+    // split-P: lane c = p*TPS + c' contributes bit slice p of bytes [E*c', E*c' + E)
+    for (int off = 1 << tps_shift; off < tpr; off <<= 1) {
+#pragma unroll
+      for (int i = 0; i < E / 4; ++i) w[i] |= __shfl_xor_sync(kFullMask, w[i], off);
+    }
+    // Output row: the input row itself, or (append) slot pos[b] + t of sequence (b, head)
+    // in a cache of `cap` token rows per sequence; tokens that fall outside are dropped.
+    int64_t orow = row;
+    bool keep = live;
+    if (am.cap > 0 && live) {
+      int64_t bh;
+      int t;
+      if (rows < (1LL << 31)) {  // 32-bit divisions: a 64-bit one is tens of instructions per thread
+        const uint32_t q = (uint32_t)row / (uint32_t)am.t_new;
+        bh = q;
+        t = (int)((uint32_t)row - q * (uint32_t)am.t_new);
+      } else {
+        bh = row / am.t_new;
+        t = (int)(row - bh * am.t_new);
+      }
+      const int64_t at = (am.pos ? (int64_t)am.pos[(uint32_t)bh / (uint32_t)am.hkv] : (int64_t)am.pos0) + t;
+      keep = at >= 0 && at < am.cap;
+      orow = bh * am.cap + at;
+    }
+    if (keep) {
+      if (p == 0) {
+        uint8_t* dst = packed + orow * (D >> LOG2P) + E * c;
+        if constexpr (E == 16) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+        }
+      }
+      if ((c & (lanes_per_group - 1)) == 0) {
+        const int64_t gi = (orow << (tpr_shift - lpg_shift)) + (c >> lpg_shift);
+        scale[gi] = sc16;
+        zero[gi] = ze16;
+      }
     }
   }
 }
@@ -167,28 +262,40 @@ __global__ void __launch_bounds__(256)
   const int64_t bh = blockIdx.x / blocks_per_seq, tb = blockIdx.x - bh * blocks_per_seq;
   const T* src = x + (bh * S + tb * kChanTok) * D + d;
   float v[kChanTok];
-  float mn, mx;
-  bool has_nan = false;
+  float mn, nmx;
 #pragma unroll
   for (int t = 0; t < kChanTok; ++t) {
     v[t] = load1<T>(src + (int64_t)t * D);
-    has_nan |= v[t] != v[t];
-    mn = t == 0 ? v[0] : fminf(mn, v[t]);
-    mx = t == 0 ? v[0] : fmaxf(mx, v[t]);
+    mn = t == 0 ? v[0] : min_nan(mn, v[t]);  // NaN propagates, as in the per-token quantiser
+    nmx = t == 0 ? -v[0] : min_nan(nmx, -v[t]);
   }
-  if (has_nan) mn = mx = __int_as_float(0x7fc00000);  // NaN propagates, as in the per-token quantiser
-  float sc = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
+  float sc = __fdiv_rn(__fsub_rn(-nmx, mn), QMAX);
   sc = (sc > 0.f) ? sc : 1.f;
   const __half sc16 = __float2half_rn(sc), ze16 = __float2half_rn(mn);
   const float scf = __half2float(sc16), zef = __half2float(ze16);
   const int64_t mrow = (bh * blocks_per_seq + tb) * D + d;
   scale[mrow] = sc16;
   zero[mrow] = ze16;
+  // codes by the reciprocal, redone with the IEEE division where one lies next to a tie (see
+  // quantize_pack_kernel)
+  constexpr float kMagic = 12582912.f;
+  const float rs = __fmul_rn(__frcp_rn(scf), 1.f / QMAX);
+  bool near_tie = false;
 #pragma unroll
   for (int t = 0; t < kChanTok; ++t) {
-    float c = rintf(__fdiv_rn(__fsub_rn(v[t], zef), scf));
-    c = fminf(fmaxf(c, 0.f), QMAX);
-    codes[t][d] = (uint8_t)(int)c;
+    const float u = __saturatef(__fmul_rn(__fsub_rn(v[t], zef), rs));
+    const float m = __fmaf_rn(u, QMAX, kMagic);
+    const float dist = __fmaf_rn(u, QMAX, -__fsub_rn(m, kMagic));
+    near_tie |= fabsf(dist) > 0.4999f;
+    codes[t][d] = (uint8_t)__float_as_uint(m);
+  }
+  if (near_tie) {
+#pragma unroll 1
+    for (int t = 0; t < kChanTok; ++t) {
+      float c = rintf(__fdiv_rn(__fsub_rn(load1<T>(src + (int64_t)t * D), zef), scf));
+      c = fminf(fmaxf(c, 0.f), QMAX);
+      codes[t][d] = (uint8_t)(int)c;
+    }
   }
   __syncthreads();
   // pack: byte j of a token = OR_p code[j + p*DP] << (p*NBITS); D threads write kChanTok*DP bytes
@@ -261,6 +368,106 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ packed,
   out[i] = from_float<T>(f);
 }
 
+// ---------------------------------------------------------------- 8 bytes per thread
+// The three kernels above as 8-byte-per-thread forms for rows whose packed width is a multiple
+// of 8 bytes (and, for dequantise, groups that are multiples of 8 dims): a thread owns packed
+// bytes [8c, 8c+8) of a row, i.e. P runs of 8 consecutive dims [p*DP + 8c, p*DP + 8c + 8).
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__half>(__half* p, const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_half2(f[0], f[1]);
+  v.y = pack_half2(f[2], f[3]);
+  v.z = pack_half2(f[4], f[5]);
+  v.w = pack_half2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  __nv_bfloat162 h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
+}
+
+template <typename T, int NBITS>
+__global__ void __launch_bounds__(256)
+    dequantize8_kernel(const uint8_t* __restrict__ packed, const __half* __restrict__ scale,
+                       const __half* __restrict__ zero, T* __restrict__ out, int64_t n_threads,
+                       int D, int gs) {
+  constexpr int P = 8 / NBITS;
+  constexpr uint32_t MASK = 0x01010101u * ((1u << NBITS) - 1);
+  const int DP = D / P, tpr = DP >> 3;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= n_threads) return;
+  const int64_t row = tid / tpr;
+  const int c = (int)(tid - row * tpr);
+  const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + row * DP + 8 * c));
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const int d0 = p * DP + 8 * c;
+    const int64_t gi = row * (D / gs) + d0 / gs;
+    const float sc = __half2float(scale[gi]), ze = __half2float(zero[gi]);
+    const uint32_t lo = (w.x >> (p * NBITS)) & MASK, hi = (w.y >> (p * NBITS)) & MASK;
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // code*scale is exact in f32 (<= 4 + 11 significant bits), so the fused form is the
+      // reference's multiply-then-add with its one rounding
+      f[i] = __fmaf_rn((float)((lo >> (8 * i)) & 0xffu), sc, ze);
+      f[4 + i] = __fmaf_rn((float)((hi >> (8 * i)) & 0xffu), sc, ze);
+    }
+    store8<T>(out + row * D + d0, f);
+  }
+}
+
+template <int NBITS>
+__global__ void __launch_bounds__(256)
+    pack_codes8_kernel(const uint8_t* __restrict__ codes, uint8_t* __restrict__ packed,
+                       int64_t n_threads, int D) {
+  constexpr int P = 8 / NBITS;
+  const int DP = D / P, tpr = DP >> 3;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= n_threads) return;
+  const int64_t row = tid / tpr;
+  const int c = (int)(tid - row * tpr);
+  uint2 w = make_uint2(0u, 0u);
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(codes + row * D + p * DP + 8 * c));
+    // a byte's bits shifted past bit 7 are dropped, like the reference's uint8 shift: clear what
+    // the 32-bit shift carried into the low bits of the next byte
+    const uint32_t keep = ~(0x01010101u * ((1u << (p * NBITS)) - 1));
+    w.x |= (v.x << (p * NBITS)) & keep;
+    w.y |= (v.y << (p * NBITS)) & keep;
+  }
+  *reinterpret_cast<uint2*>(packed + row * DP + 8 * c) = w;
+}
+
+template <int NBITS>
+__global__ void __launch_bounds__(256)
+    unpack_codes8_kernel(const uint8_t* __restrict__ packed, uint8_t* __restrict__ codes,
+                         int64_t n_threads, int D) {
+  constexpr int P = 8 / NBITS;
+  constexpr uint32_t MASK = 0x01010101u * ((1u << NBITS) - 1);
+  const int DP = D / P, tpr = DP >> 3;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid >= n_threads) return;
+  const int64_t row = tid / tpr;
+  const int c = (int)(tid - row * tpr);
+  const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + row * DP + 8 * c));
+#pragma unroll
+  for (int p = 0; p < P; ++p)
+    *reinterpret_cast<uint2*>(codes + row * D + p * DP + 8 * c) =
+        make_uint2((w.x >> (p * NBITS)) & MASK, (w.y >> (p * NBITS)) & MASK);
+}
+
 inline bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 
 }  // namespace tkv
@@ -279,6 +486,16 @@ extern "C" int tkv_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t row
   if (n == 0) return TKV_OK;  // an empty tensor has no storage: nothing to check, nothing to do
   TKV_REQUIRE(codes && packed, TKV_ERR_INVALID, "pack_codes: null pointer");
   TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "pack_codes: tensor too large");
+  if ((D / P) % 8 == 0 && ((uintptr_t)codes & 7u) == 0 && ((uintptr_t)packed & 7u) == 0) {
+    const int64_t nt = n / 8;
+    const int blocks8 = (int)((nt + 255) / 256);
+    if (nbits == 4)
+      pack_codes8_kernel<4><<<blocks8, 256, 0, (cudaStream_t)stream>>>(codes, packed, nt, D);
+    else
+      pack_codes8_kernel<2><<<blocks8, 256, 0, (cudaStream_t)stream>>>(codes, packed, nt, D);
+    TKV_CUDA(cudaGetLastError());
+    return TKV_OK;
+  }
   const int blocks = (int)((n + 255) / 256);
   if (nbits == 4)
     pack_codes_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(codes, packed, n, D);
@@ -299,6 +516,16 @@ extern "C" int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t r
   if (n == 0) return TKV_OK;
   TKV_REQUIRE(codes && packed, TKV_ERR_INVALID, "unpack_codes: null pointer");
   TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "unpack_codes: tensor too large");
+  if ((D / P) % 8 == 0 && ((uintptr_t)codes & 7u) == 0 && ((uintptr_t)packed & 7u) == 0) {
+    const int64_t nt = rows * (D / P / 8);
+    const int blocks8 = (int)((nt + 255) / 256);
+    if (nbits == 4)
+      unpack_codes8_kernel<4><<<blocks8, 256, 0, (cudaStream_t)stream>>>(packed, codes, nt, D);
+    else
+      unpack_codes8_kernel<2><<<blocks8, 256, 0, (cudaStream_t)stream>>>(packed, codes, nt, D);
+    TKV_CUDA(cudaGetLastError());
+    return TKV_OK;
+  }
   const int blocks = (int)((n + 255) / 256);
   if (nbits == 4)
     unpack_codes_kernel<4><<<blocks, 256, 0, (cudaStream_t)stream>>>(packed, codes, n, D);
@@ -309,20 +536,38 @@ extern "C" int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t r
 }
 
 namespace {
+inline int log2i(int v) {
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+template <typename T, int E>
+int launch_quantize_e(const void* x, uint8_t* packed, void* scale, void* zero, int64_t rows, int D,
+                      int nbits, int gs, cudaStream_t stream, const AppendMap& am) {
+  const int tpr_shift = log2i(D / E), lpg_shift = log2i(gs / E);  // powers of two, checked by the caller
+  const int rows_per_block = kRowsPerThread * (256 >> tpr_shift);
+  const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+  TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "quantize_pack: tensor too large");
+  if (nbits == 4)
+    quantize_pack_kernel<T, 4, E><<<(int)blocks, 256, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, tpr_shift, lpg_shift, am);
+  else
+    quantize_pack_kernel<T, 2, E><<<(int)blocks, 256, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, tpr_shift, lpg_shift, am);
+  TKV_CUDA(cudaGetLastError());
+  return TKV_OK;
+}
+
 template <typename T>
 int launch_quantize(const void* x, uint8_t* packed, void* scale, void* zero, int64_t rows, int D,
                     int nbits, int gs, cudaStream_t stream, const AppendMap am = AppendMap{}) {
-  const int64_t threads = rows * (D / 8);
-  const int64_t blocks = (threads + 255) / 256;
-  TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "quantize_pack: tensor too large");
-  if (nbits == 4)
-    quantize_pack_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs, am);
-  else
-    quantize_pack_kernel<T, 2><<<(int)blocks, 256, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, rows, D, gs, am);
-  TKV_CUDA(cudaGetLastError());
-  return TKV_OK;
+  // 16 elements per thread where a 16-bit row gives every bit slice and every group a whole thread
+  if constexpr (!std::is_same<T, float>::value) {
+    if (gs >= 16 && D / 16 >= 8 / nbits && ((uintptr_t)packed & 15u) == 0)
+      return launch_quantize_e<T, 16>(x, packed, scale, zero, rows, D, nbits, gs, stream, am);
+  }
+  return launch_quantize_e<T, 8>(x, packed, scale, zero, rows, D, nbits, gs, stream, am);
 }
 }  // namespace
 
@@ -382,6 +627,8 @@ extern "C" int tkv_quantize_append(const void* x, int in_dtype, uint8_t* packed,
               "quantize_append: tokens [%d, %d) do not fit a cache of %lld rows", pos0, pos0 + T_new,
               (long long)S_cap);
   if (T_new == 0) return TKV_OK;
+  TKV_REQUIRE((int64_t)B * HKV < (1LL << 31), TKV_ERR_INVALID,
+              "quantize_append: B*HKV = %lld sequences x heads exceed 2^31", (long long)B * HKV);
   AppendMap am{positions, pos0, T_new, HKV, S_cap};
   const int64_t rows = (int64_t)B * HKV * T_new;
   cudaStream_t s = (cudaStream_t)stream;
@@ -401,6 +648,19 @@ int launch_dequant(const uint8_t* packed, const void* scale, const void* zero, v
   const int64_t n = rows * D;
   const int64_t blocks = (n + 255) / 256;
   TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "dequantize: tensor too large");
+  const int DP = D / (8 / nbits);
+  if (DP % 8 == 0 && gs % 8 == 0 && ((uintptr_t)packed & 7u) == 0 && aligned16(out)) {
+    const int64_t nt = rows * (DP / 8);
+    const int blocks8 = (int)((nt + 255) / 256);
+    if (nbits == 4)
+      dequantize8_kernel<T, 4><<<blocks8, 256, 0, stream>>>(packed, (const __half*)scale,
+                                                            (const __half*)zero, (T*)out, nt, D, gs);
+    else
+      dequantize8_kernel<T, 2><<<blocks8, 256, 0, stream>>>(packed, (const __half*)scale,
+                                                            (const __half*)zero, (T*)out, nt, D, gs);
+    TKV_CUDA(cudaGetLastError());
+    return TKV_OK;
+  }
   if (nbits == 4)
     dequantize_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(packed, (const __half*)scale,
                                                              (const __half*)zero, (T*)out, n, D, gs);
