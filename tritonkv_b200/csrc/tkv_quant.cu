@@ -67,6 +67,27 @@ __device__ __forceinline__ H2 fold_minmax(H2 a, H2 b) {
   return __hmin2_nan(*reinterpret_cast<const H2*>(&lo), *reinterpret_cast<const H2*>(&hi));
 }
 
+// (x.lo - z, x.hi - z) in f32 from a packed pair of 16-bit values: the mixed-precision subtract of
+// sm_100 widens the 16-bit operand itself, so no conversion instruction is spent per element.
+template <typename H2>
+__device__ __forceinline__ float2 sub_widen(H2 x, float z);
+template <>
+__device__ __forceinline__ float2 sub_widen<__half2>(__half2 x, float z) {
+  float2 r;
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tsub.rn.f32.f16 %0, l, %3;\n\tsub.rn.f32.f16 %1, h, %3;\n\t}"
+      : "=f"(r.x), "=f"(r.y)
+      : "r"(*reinterpret_cast<const uint32_t*>(&x)), "f"(z));
+  return r;
+}
+template <>
+__device__ __forceinline__ float2 sub_widen<__nv_bfloat162>(__nv_bfloat162 x, float z) {
+  float2 r;
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tsub.rn.f32.bf16 %0, l, %3;\n\tsub.rn.f32.bf16 %1, h, %3;\n\t}"
+      : "=f"(r.x), "=f"(r.y)
+      : "r"(*reinterpret_cast<const uint32_t*>(&x)), "f"(z));
+  return r;
+}
+
 // Where the rows go when new tokens are appended to a preallocated cache (cap == 0: in place).
 struct AppendMap {
   const int32_t* pos;  // per-sequence first free slot, or null for pos0 everywhere
@@ -104,19 +125,14 @@ __global__ void __launch_bounds__(256)
     // Lanes past the end mirror the last row so the shuffles below stay full-warp.
     const int64_t r = live ? row : rows - 1;
     const T* src = x + r * D + E * c;
-    float v[E], mn, nmx;
+    float a[E], mn, nmx;  // a: the elements (f32 rows) and then x - zero
+    [[maybe_unused]] uint32_t raw[k16 ? E / 2 : 1];  // 16-bit rows: the elements as loaded
     if constexpr (k16) {
       using H2 = typename Pair16<T>::type;
       H2 h[E / 2];
 #pragma unroll
       for (int i = 0; i < E / 8; ++i)
         *reinterpret_cast<uint4*>(&h[4 * i]) = __ldg(reinterpret_cast<const uint4*>(src) + i);
-#pragma unroll
-      for (int i = 0; i < E / 2; ++i) {
-        const float2 f = widen2<H2>(h[i]);
-        v[2 * i] = f.x;
-        v[2 * i + 1] = f.y;
-      }
       H2 lo = h[0], hi = h[0];
 #pragma unroll
       for (int i = 1; i < E / 2; ++i) {
@@ -131,17 +147,19 @@ __global__ void __launch_bounds__(256)
       const float2 f = widen2<H2>(pm);
       mn = f.x;
       nmx = f.y;
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) raw[i] = *reinterpret_cast<const uint32_t*>(&h[i]);
     } else {
-      const float4 a = __ldg(reinterpret_cast<const float4*>(src));
-      const float4 b = __ldg(reinterpret_cast<const float4*>(src) + 1);
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-      mn = v[0];
-      nmx = -v[0];
+      const float4 lo4 = __ldg(reinterpret_cast<const float4*>(src));
+      const float4 hi4 = __ldg(reinterpret_cast<const float4*>(src) + 1);
+      a[0] = lo4.x; a[1] = lo4.y; a[2] = lo4.z; a[3] = lo4.w;
+      a[4] = hi4.x; a[5] = hi4.y; a[6] = hi4.z; a[7] = hi4.w;
+      mn = a[0];
+      nmx = -a[0];
 #pragma unroll
       for (int i = 1; i < 8; ++i) {
-        mn = min_nan(mn, v[i]);
-        nmx = min_nan(nmx, -v[i]);
+        mn = min_nan(mn, a[i]);
+        nmx = min_nan(nmx, -a[i]);
       }
       for (int off = 1; off < lanes_per_group; off <<= 1) {
         mn = min_nan(mn, __shfl_xor_sync(kFullMask, mn, off));
@@ -159,11 +177,23 @@ __global__ void __launch_bounds__(256)
     const float scf = __half2float(sc16), zef = __half2float(ze16);
     const float rs = __fmul_rn(rcp_approx(scf), 1.f / QMAX);  // a * rs = quotient / QMAX, saturated to [0, 1]
 
+    if constexpr (k16) {
+      using H2 = typename Pair16<T>::type;
+#pragma unroll
+      for (int i = 0; i < E / 2; ++i) {
+        const float2 d = sub_widen<H2>(*reinterpret_cast<const H2*>(&raw[i]), zef);
+        a[2 * i] = d.x;
+        a[2 * i + 1] = d.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < E; ++i) a[i] = __fsub_rn(a[i], zef);
+    }
     float m[E];
     bool near_tie = false;
 #pragma unroll
     for (int i = 0; i < E; ++i) {
-      const float u = __saturatef(__fmul_rn(__fsub_rn(v[i], zef), rs));  // NaN -> 0, as the clamp gives
+      const float u = __saturatef(__fmul_rn(a[i], rs));                  // NaN -> 0, as the clamp gives
       m[i] = __fmaf_rn(u, QMAX, kMagic);
       const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));      // distance to the integer taken
       near_tie |= fabsf(d) > 0.4999f;
@@ -171,10 +201,10 @@ __global__ void __launch_bounds__(256)
     if (near_tie) {  // a minority of the warps comes here, for one element or two
 #pragma unroll
       for (int i = 0; i < E; ++i) {
-        const float u = __saturatef(__fmul_rn(__fsub_rn(v[i], zef), rs));
+        const float u = __saturatef(__fmul_rn(a[i], rs));
         const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));
         if (fabsf(d) > 0.4999f) {
-          float t = rintf(__fdiv_rn(__fsub_rn(v[i], zef), scf));
+          float t = rintf(__fdiv_rn(a[i], scf));
           t = fminf(fmaxf(t, 0.f), QMAX);
           m[i] = __fadd_rn(t, kMagic);
         }
@@ -396,76 +426,131 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
 }
 
+// Items (8 packed bytes each) are dealt to a block kItemsPerThread * 256 at a time, thread t taking
+// items t, t + 256, ...: every load of a warp is contiguous and a thread has several in flight.
+constexpr int kItemsPerThread = 4;
+
+// item -> (row, column block) with a 32-bit division where the tensor allows it (a 64-bit one is
+// tens of instructions)
+__device__ __forceinline__ void item_row_col(int64_t it, int tpr, bool small, int64_t& row, int& c) {
+  if (small) {
+    const uint32_t q = (uint32_t)it / (uint32_t)tpr;
+    row = q;
+    c = (int)((uint32_t)it - q * (uint32_t)tpr);
+  } else {
+    row = it / tpr;
+    c = (int)(it - row * tpr);
+  }
+}
+
 template <typename T, int NBITS>
 __global__ void __launch_bounds__(256)
     dequantize8_kernel(const uint8_t* __restrict__ packed, const __half* __restrict__ scale,
-                       const __half* __restrict__ zero, T* __restrict__ out, int64_t n_threads,
+                       const __half* __restrict__ zero, T* __restrict__ out, int64_t n_items,
                        int D, int gs) {
   constexpr int P = 8 / NBITS;
   constexpr uint32_t MASK = 0x01010101u * ((1u << NBITS) - 1);
-  const int DP = D / P, tpr = DP >> 3;
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (tid >= n_threads) return;
-  const int64_t row = tid / tpr;
-  const int c = (int)(tid - row * tpr);
-  const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + row * DP + 8 * c));
+  const int DP = D / P, tpr = DP >> 3, ng = D / gs;
+  const bool gs_pow2 = (gs & (gs - 1)) == 0;
+  const int gs_shift = __ffs(gs) - 1;
+  const int64_t base = (int64_t)blockIdx.x * (kItemsPerThread * 256) + threadIdx.x;
+  uint2 w[kItemsPerThread];
+  int64_t row[kItemsPerThread];
+  int c[kItemsPerThread];
 #pragma unroll
-  for (int p = 0; p < P; ++p) {
-    const int d0 = p * DP + 8 * c;
-    const int64_t gi = row * (D / gs) + d0 / gs;
-    const float sc = __half2float(scale[gi]), ze = __half2float(zero[gi]);
-    const uint32_t lo = (w.x >> (p * NBITS)) & MASK, hi = (w.y >> (p * NBITS)) & MASK;
-    float f[8];
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    const int64_t item = base + k * 256;
+    const int64_t it = item < n_items ? item : n_items - 1;
+    item_row_col(it, tpr, n_items < (1LL << 31), row[k], c[k]);
+    w[k] = __ldg(reinterpret_cast<const uint2*>(packed + row[k] * DP + 8 * c[k]));
+  }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      // code*scale is exact in f32 (<= 4 + 11 significant bits), so the fused form is the
-      // reference's multiply-then-add with its one rounding
-      f[i] = __fmaf_rn((float)((lo >> (8 * i)) & 0xffu), sc, ze);
-      f[4 + i] = __fmaf_rn((float)((hi >> (8 * i)) & 0xffu), sc, ze);
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    if (base + k * 256 >= n_items) break;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int d0 = p * DP + 8 * c[k];
+      const int64_t gi = row[k] * ng + (gs_pow2 ? d0 >> gs_shift : d0 / gs);
+      const float sc = __half2float(scale[gi]), ze = __half2float(zero[gi]);
+      const uint32_t lo = (w[k].x >> (p * NBITS)) & MASK, hi = (w[k].y >> (p * NBITS)) & MASK;
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // code*scale is exact in f32 (<= 4 + 11 significant bits), so the fused form is the
+        // reference's multiply-then-add with its one rounding
+        f[i] = __fmaf_rn((float)((lo >> (8 * i)) & 0xffu), sc, ze);
+        f[4 + i] = __fmaf_rn((float)((hi >> (8 * i)) & 0xffu), sc, ze);
+      }
+      store8<T>(out + row[k] * D + d0, f);
     }
-    store8<T>(out + row * D + d0, f);
   }
 }
 
 template <int NBITS>
 __global__ void __launch_bounds__(256)
     pack_codes8_kernel(const uint8_t* __restrict__ codes, uint8_t* __restrict__ packed,
-                       int64_t n_threads, int D) {
+                       int64_t n_items, int D) {
   constexpr int P = 8 / NBITS;
   const int DP = D / P, tpr = DP >> 3;
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (tid >= n_threads) return;
-  const int64_t row = tid / tpr;
-  const int c = (int)(tid - row * tpr);
-  uint2 w = make_uint2(0u, 0u);
+  const int64_t base = (int64_t)blockIdx.x * (kItemsPerThread * 256) + threadIdx.x;
+  uint2 v[kItemsPerThread][P];
+  int64_t off[kItemsPerThread];
 #pragma unroll
-  for (int p = 0; p < P; ++p) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(codes + row * D + p * DP + 8 * c));
-    // a byte's bits shifted past bit 7 are dropped, like the reference's uint8 shift: clear what
-    // the 32-bit shift carried into the low bits of the next byte
-    const uint32_t keep = ~(0x01010101u * ((1u << (p * NBITS)) - 1));
-    w.x |= (v.x << (p * NBITS)) & keep;
-    w.y |= (v.y << (p * NBITS)) & keep;
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    const int64_t item = base + k * 256;
+    const int64_t it = item < n_items ? item : n_items - 1;
+    int64_t row;
+    int c;
+    item_row_col(it, tpr, n_items < (1LL << 31), row, c);
+    off[k] = row * DP + 8 * c;
+#pragma unroll
+    for (int p = 0; p < P; ++p)
+      v[k][p] = __ldg(reinterpret_cast<const uint2*>(codes + row * D + p * DP + 8 * c));
   }
-  *reinterpret_cast<uint2*>(packed + row * DP + 8 * c) = w;
+#pragma unroll
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    if (base + k * 256 >= n_items) break;
+    uint2 w = make_uint2(0u, 0u);
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      // a byte's bits shifted past bit 7 are dropped, like the reference's uint8 shift: clear what
+      // the 32-bit shift carried into the low bits of the next byte
+      const uint32_t keep = ~(0x01010101u * ((1u << (p * NBITS)) - 1));
+      w.x |= (v[k][p].x << (p * NBITS)) & keep;
+      w.y |= (v[k][p].y << (p * NBITS)) & keep;
+    }
+    *reinterpret_cast<uint2*>(packed + off[k]) = w;
+  }
 }
 
 template <int NBITS>
 __global__ void __launch_bounds__(256)
     unpack_codes8_kernel(const uint8_t* __restrict__ packed, uint8_t* __restrict__ codes,
-                         int64_t n_threads, int D) {
+                         int64_t n_items, int D) {
   constexpr int P = 8 / NBITS;
   constexpr uint32_t MASK = 0x01010101u * ((1u << NBITS) - 1);
   const int DP = D / P, tpr = DP >> 3;
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (tid >= n_threads) return;
-  const int64_t row = tid / tpr;
-  const int c = (int)(tid - row * tpr);
-  const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + row * DP + 8 * c));
+  const int64_t base = (int64_t)blockIdx.x * (kItemsPerThread * 256) + threadIdx.x;
+  uint2 w[kItemsPerThread];
+  int64_t off[kItemsPerThread];
 #pragma unroll
-  for (int p = 0; p < P; ++p)
-    *reinterpret_cast<uint2*>(codes + row * D + p * DP + 8 * c) =
-        make_uint2((w.x >> (p * NBITS)) & MASK, (w.y >> (p * NBITS)) & MASK);
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    const int64_t item = base + k * 256;
+    const int64_t it = item < n_items ? item : n_items - 1;
+    int64_t row;
+    int c;
+    item_row_col(it, tpr, n_items < (1LL << 31), row, c);
+    off[k] = row * D + 8 * c;
+    w[k] = __ldg(reinterpret_cast<const uint2*>(packed + row * DP + 8 * c));
+  }
+#pragma unroll
+  for (int k = 0; k < kItemsPerThread; ++k) {
+    if (base + k * 256 >= n_items) break;
+#pragma unroll
+    for (int p = 0; p < P; ++p)
+      *reinterpret_cast<uint2*>(codes + off[k] + p * DP) =
+          make_uint2((w[k].x >> (p * NBITS)) & MASK, (w[k].y >> (p * NBITS)) & MASK);
+  }
 }
 
 inline bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
@@ -488,7 +573,7 @@ extern "C" int tkv_pack_codes(const uint8_t* codes, uint8_t* packed, int64_t row
   TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "pack_codes: tensor too large");
   if ((D / P) % 8 == 0 && ((uintptr_t)codes & 7u) == 0 && ((uintptr_t)packed & 7u) == 0) {
     const int64_t nt = n / 8;
-    const int blocks8 = (int)((nt + 255) / 256);
+    const int blocks8 = (int)((nt + kItemsPerThread * 256 - 1) / (kItemsPerThread * 256));
     if (nbits == 4)
       pack_codes8_kernel<4><<<blocks8, 256, 0, (cudaStream_t)stream>>>(codes, packed, nt, D);
     else
@@ -518,7 +603,7 @@ extern "C" int tkv_unpack_codes(const uint8_t* packed, uint8_t* codes, int64_t r
   TKV_REQUIRE((n + 255) / 256 <= 0x7fffffffLL, TKV_ERR_INVALID, "unpack_codes: tensor too large");
   if ((D / P) % 8 == 0 && ((uintptr_t)codes & 7u) == 0 && ((uintptr_t)packed & 7u) == 0) {
     const int64_t nt = rows * (D / P / 8);
-    const int blocks8 = (int)((nt + 255) / 256);
+    const int blocks8 = (int)((nt + kItemsPerThread * 256 - 1) / (kItemsPerThread * 256));
     if (nbits == 4)
       unpack_codes8_kernel<4><<<blocks8, 256, 0, (cudaStream_t)stream>>>(packed, codes, nt, D);
     else
@@ -651,7 +736,7 @@ int launch_dequant(const uint8_t* packed, const void* scale, const void* zero, v
   const int DP = D / (8 / nbits);
   if (DP % 8 == 0 && gs % 8 == 0 && ((uintptr_t)packed & 7u) == 0 && aligned16(out)) {
     const int64_t nt = rows * (DP / 8);
-    const int blocks8 = (int)((nt + 255) / 256);
+    const int blocks8 = (int)((nt + kItemsPerThread * 256 - 1) / (kItemsPerThread * 256));
     if (nbits == 4)
       dequantize8_kernel<T, 4><<<blocks8, 256, 0, stream>>>(packed, (const __half*)scale,
                                                             (const __half*)zero, (T*)out, nt, D, gs);
