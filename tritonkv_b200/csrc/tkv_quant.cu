@@ -190,33 +190,45 @@ __global__ void __launch_bounds__(256)
       for (int i = 0; i < E; ++i) a[i] = __fsub_rn(a[i], zef);
     }
     float m[E];
-    bool near_tie = false;
+    uint32_t near_tie = 0;  // bit i: element i lies next to a tie
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       const float u = __saturatef(__fmul_rn(a[i], rs));                  // NaN -> 0, as the clamp gives
       m[i] = __fmaf_rn(u, QMAX, kMagic);
       const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));      // distance to the integer taken
-      near_tie |= fabsf(d) > 0.4999f;
-    }
-    if (near_tie) {  // a minority of the warps comes here, for one element or two
-#pragma unroll
-      for (int i = 0; i < E; ++i) {
-        const float u = __saturatef(__fmul_rn(a[i], rs));
-        const float d = __fmaf_rn(u, QMAX, -__fsub_rn(m[i], kMagic));
-        if (fabsf(d) > 0.4999f) {
-          float t = rintf(__fdiv_rn(a[i], scf));
-          t = fminf(fmaxf(t, 0.f), QMAX);
-          m[i] = __fadd_rn(t, kMagic);
-        }
-      }
+      if (fabsf(d) > 0.4999f) near_tie |= 1u << i;
     }
     uint32_t w[E / 4];  // codes, one per byte
 #pragma unroll
     for (int i = 0; i < E / 4; ++i) {
-      const uint32_t a = __byte_perm(__float_as_uint(m[4 * i]), __float_as_uint(m[4 * i + 1]), 0x0040);
-      const uint32_t b = __byte_perm(__float_as_uint(m[4 * i + 2]), __float_as_uint(m[4 * i + 3]), 0x0040);
-      w[i] = __byte_perm(a, b, 0x5410) << (NBITS * p);
+      const uint32_t lo2 = __byte_perm(__float_as_uint(m[4 * i]), __float_as_uint(m[4 * i + 1]), 0x0040);
+      const uint32_t hi2 = __byte_perm(__float_as_uint(m[4 * i + 2]), __float_as_uint(m[4 * i + 3]), 0x0040);
+      w[i] = __byte_perm(lo2, hi2, 0x5410);
     }
+    // About one thread in a hundred has such an element (a third of the warps): those codes are
+    // redone with the IEEE division from the element as stored and put into their byte.
+    while (near_tie) {
+      const int i = __ffs(near_tie) - 1;
+      near_tie &= near_tie - 1;
+      float xi;
+      if constexpr (std::is_same<T, float>::value) {
+        xi = src[i];
+      } else if constexpr (std::is_same<T, __half>::value) {
+        xi = __half2float(src[i]);
+      } else {
+        xi = __bfloat162float(src[i]);
+      }
+      float t = rintf(__fdiv_rn(__fsub_rn(xi, zef), scf));
+      t = fminf(fmaxf(t, 0.f), QMAX);
+      const uint32_t sh = (i & 3) * 8, code = (uint32_t)(int)t << sh, byte = 0xffu << sh;
+#pragma unroll
+      for (int k = 0; k < E / 4; ++k) {  // masks, not an indexed store: w stays in registers
+        const uint32_t sel = (k == (i >> 2)) ? byte : 0u;
+        w[k] = (w[k] & ~sel) | (code & sel);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < E / 4; ++i) w[i] <<= (NBITS * p);
     // split-P: lane c = p*TPS + c' contributes bit slice p of bytes [E*c', E*c' + E)
     for (int off = 1 << tps_shift; off < tpr; off <<= 1) {
 #pragma unroll
@@ -265,77 +277,154 @@ __global__ void __launch_bounds__(256)
 // no implementation of it).  Same per-element arithmetic as quantize_pack_kernel on the other
 // axis; the codes keep the split-P byte layout along the head dimension, scale and zero are
 // one row of D values per block of kChanTok tokens.
-// One CTA per (sequence x head, token block), one thread per head dimension: the thread walks
-// the block's tokens of its dimension (the loads of a warp are one contiguous row piece),
-// derives scale/zero, leaves its codes in shared memory, and the CTA then packs whole rows.
+// A CTA of 256 threads takes 512/D consecutive token blocks; a thread owns two adjacent head
+// dimensions of one block and walks its 32 tokens (4-byte loads of a 16-bit row, contiguous
+// across the warp), keeps min and max per dimension as packed pairs, derives the two scales and
+// zeros, leaves its codes in shared memory, and the CTA then packs whole rows, 16 bytes per
+// thread and store.
 constexpr int kChanTok = 32;
 
+// One dimension's scale, zero and reciprocal from its (min, max).
+struct ChanScale {
+  __half sc16, ze16;
+  float scf, zef, rs;
+};
+template <int NBITS>
+__device__ __forceinline__ ChanScale chan_scale(float mn, float mx) {
+  constexpr float QMAX = float((1 << NBITS) - 1);
+  ChanScale r;
+  float sc = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
+  sc = (sc > 0.f) ? sc : 1.f;
+  r.sc16 = __float2half_rn(sc);
+  r.ze16 = __float2half_rn(mn);
+  r.scf = __half2float(r.sc16);
+  r.zef = __half2float(r.ze16);
+  r.rs = __fmul_rn(rcp_approx(r.scf), 1.f / QMAX);
+  return r;
+}
+
+// The two elements of one token as f32 (the loads of the second pass hit L1/L2).
 template <typename T>
-__device__ __forceinline__ float load1(const T* p) { return (float)*p; }
+__device__ __forceinline__ float2 load2(const T* p);
 template <>
-__device__ __forceinline__ float load1<__half>(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
 template <>
-__device__ __forceinline__ float load1<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return __bfloat162float(*p);
+__device__ __forceinline__ float2 load2<__half>(const __half* p) {
+  return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
+template <>
+__device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
 }
 
 template <typename T, int NBITS>
 __global__ void __launch_bounds__(256)
     quantize_keys_channel_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed,
                                  __half* __restrict__ scale, __half* __restrict__ zero,
-                                 int64_t S, int64_t S_q, int D) {
+                                 int64_t S, int64_t S_q, int D, int64_t n_blocks) {
   constexpr int P = 8 / NBITS;
   constexpr float QMAX = float((1 << NBITS) - 1);
-  __shared__ uint8_t codes[kChanTok][256];
-  const int d = threadIdx.x;
-  const int64_t blocks_per_seq = S_q / kChanTok;
-  const int64_t bh = blockIdx.x / blocks_per_seq, tb = blockIdx.x - bh * blocks_per_seq;
-  const T* src = x + (bh * S + tb * kChanTok) * D + d;
-  float v[kChanTok];
-  float mn, nmx;
-#pragma unroll
-  for (int t = 0; t < kChanTok; ++t) {
-    v[t] = load1<T>(src + (int64_t)t * D);
-    mn = t == 0 ? v[0] : min_nan(mn, v[t]);  // NaN propagates, as in the per-token quantiser
-    nmx = t == 0 ? -v[0] : min_nan(nmx, -v[t]);
-  }
-  float sc = __fdiv_rn(__fsub_rn(-nmx, mn), QMAX);
-  sc = (sc > 0.f) ? sc : 1.f;
-  const __half sc16 = __float2half_rn(sc), ze16 = __float2half_rn(mn);
-  const float scf = __half2float(sc16), zef = __half2float(ze16);
-  const int64_t mrow = (bh * blocks_per_seq + tb) * D + d;
-  scale[mrow] = sc16;
-  zero[mrow] = ze16;
-  // codes by the reciprocal, redone with the IEEE division where one lies next to a tie (see
-  // quantize_pack_kernel)
   constexpr float kMagic = 12582912.f;
-  const float rs = __fmul_rn(__frcp_rn(scf), 1.f / QMAX);
-  bool near_tie = false;
+  constexpr bool k16 = !std::is_same<T, float>::value;
+  __shared__ __align__(16) uint8_t codes[512 * kChanTok];  // [local block][token][dim]
+  const int tpb = D >> 1;                                   // threads per token block
+  const int nb = 256 / tpb;                                 // token blocks per CTA
+  const int lb = threadIdx.x / tpb, dp = threadIdx.x - lb * tpb;
+  const int64_t blocks_per_seq = S_q / kChanTok;
+  const int64_t gb = (int64_t)blockIdx.x * nb + lb;
+  if (gb < n_blocks) {
+    const int64_t bh = gb / blocks_per_seq, tb = gb - bh * blocks_per_seq;
+    const T* src = x + (bh * S + tb * kChanTok) * D + 2 * dp;
+    float mn0, mn1, mx0, mx1;
+    [[maybe_unused]] uint32_t raw[k16 ? kChanTok : 1];
+    if constexpr (k16) {
+      using H2 = typename Pair16<T>::type;
+      H2 lo, hi;
 #pragma unroll
-  for (int t = 0; t < kChanTok; ++t) {
-    const float u = __saturatef(__fmul_rn(__fsub_rn(v[t], zef), rs));
-    const float m = __fmaf_rn(u, QMAX, kMagic);
-    const float dist = __fmaf_rn(u, QMAX, -__fsub_rn(m, kMagic));
-    near_tie |= fabsf(dist) > 0.4999f;
-    codes[t][d] = (uint8_t)__float_as_uint(m);
-  }
-  if (near_tie) {
-#pragma unroll 1
+      for (int t = 0; t < kChanTok; ++t) {
+        raw[t] = __ldg(reinterpret_cast<const uint32_t*>(src + (int64_t)t * D));
+        const H2 h = *reinterpret_cast<const H2*>(&raw[t]);
+        lo = t == 0 ? h : __hmin2_nan(lo, h);  // NaN propagates, as in the per-token quantiser
+        hi = t == 0 ? h : __hmax2_nan(hi, h);
+      }
+      const float2 l = widen2<H2>(lo), u = widen2<H2>(hi);
+      mn0 = l.x; mn1 = l.y; mx0 = u.x; mx1 = u.y;
+    } else {
+      float n0, n1;  // -max
+#pragma unroll
+      for (int t = 0; t < kChanTok; ++t) {
+        const float2 v = __ldg(reinterpret_cast<const float2*>(src + (int64_t)t * D));
+        mn0 = t == 0 ? v.x : min_nan(mn0, v.x);
+        mn1 = t == 0 ? v.y : min_nan(mn1, v.y);
+        n0 = t == 0 ? -v.x : min_nan(n0, -v.x);
+        n1 = t == 0 ? -v.y : min_nan(n1, -v.y);
+      }
+      mx0 = -n0;
+      mx1 = -n1;
+    }
+    const ChanScale c0 = chan_scale<NBITS>(mn0, mx0), c1 = chan_scale<NBITS>(mn1, mx1);
+    const int64_t mrow = gb * D + 2 * dp;
+    *reinterpret_cast<__half2*>(scale + mrow) = __halves2half2(c0.sc16, c1.sc16);
+    *reinterpret_cast<__half2*>(zero + mrow) = __halves2half2(c0.ze16, c1.ze16);
+    // codes by the reciprocal, those next to a tie redone with the IEEE division (see
+    // quantize_pack_kernel)
+    uint8_t* crow = codes + (lb * kChanTok) * D + 2 * dp;
+    uint32_t near_tie = 0;  // bit t: token t holds a code next to a tie
+#pragma unroll
     for (int t = 0; t < kChanTok; ++t) {
-      float c = rintf(__fdiv_rn(__fsub_rn(load1<T>(src + (int64_t)t * D), zef), scf));
-      c = fminf(fmaxf(c, 0.f), QMAX);
-      codes[t][d] = (uint8_t)(int)c;
+      float a0, a1;
+      if constexpr (k16) {
+        using H2 = typename Pair16<T>::type;
+        const float2 v = widen2<H2>(*reinterpret_cast<const H2*>(&raw[t]));
+        a0 = __fsub_rn(v.x, c0.zef);
+        a1 = __fsub_rn(v.y, c1.zef);
+      } else {
+        const float2 v = __ldg(reinterpret_cast<const float2*>(src + (int64_t)t * D));
+        a0 = __fsub_rn(v.x, c0.zef);
+        a1 = __fsub_rn(v.y, c1.zef);
+      }
+      const float u0 = __saturatef(__fmul_rn(a0, c0.rs)), u1 = __saturatef(__fmul_rn(a1, c1.rs));
+      const float m0 = __fmaf_rn(u0, QMAX, kMagic), m1 = __fmaf_rn(u1, QMAX, kMagic);
+      const float d0 = __fmaf_rn(u0, QMAX, -__fsub_rn(m0, kMagic));
+      const float d1 = __fmaf_rn(u1, QMAX, -__fsub_rn(m1, kMagic));
+      if (fabsf(d0) > 0.4999f || fabsf(d1) > 0.4999f) near_tie |= 1u << t;
+      *reinterpret_cast<uint16_t*>(crow + t * D) =
+          (uint16_t)__byte_perm(__float_as_uint(m0), __float_as_uint(m1), 0x0040);
+    }
+    // about one thread in twenty has such a token, so most warps come here -- for one token or two
+    while (near_tie) {
+      const int t = __ffs(near_tie) - 1;
+      near_tie &= near_tie - 1;
+      {
+        const float2 v = load2<T>(src + (int64_t)t * D);
+        float q0 = rintf(__fdiv_rn(__fsub_rn(v.x, c0.zef), c0.scf));
+        float q1 = rintf(__fdiv_rn(__fsub_rn(v.y, c1.zef), c1.scf));
+        q0 = fminf(fmaxf(q0, 0.f), QMAX);
+        q1 = fminf(fmaxf(q1, 0.f), QMAX);
+        *reinterpret_cast<uint16_t*>(crow + t * D) = (uint16_t)((int)q0 | ((int)q1 << 8));
+      }
     }
   }
   __syncthreads();
-  // pack: byte j of a token = OR_p code[j + p*DP] << (p*NBITS); D threads write kChanTok*DP bytes
+  // pack: byte j of a token = OR_p code[j + p*DP] << (p*NBITS); a thread makes 16 bytes at a time
   const int DP = D / P;
-  for (int i = threadIdx.x; i < kChanTok * DP; i += blockDim.x) {
-    const int t = i / DP, j = i - t * DP;
-    uint32_t b = 0;
+  const int chunks_per_row = DP >> 4;  // DP >= 16 (checked by the caller)
+  const int n_chunks = nb * kChanTok * chunks_per_row;
+  for (int i = threadIdx.x; i < n_chunks; i += 256) {
+    const int rowl = i / chunks_per_row, j = (i - rowl * chunks_per_row) << 4;  // row = local block * 32 + token
+    const int64_t g = (int64_t)blockIdx.x * nb + rowl / kChanTok;
+    if (g >= n_blocks) break;  // local blocks are in order: the rest is past the end too
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int p = 0; p < P; ++p) b |= (uint32_t)codes[t][j + p * DP] << (p * NBITS);
-    packed[((bh * S_q) + tb * kChanTok + t) * DP + j] = (uint8_t)b;
+    for (int p = 0; p < P; ++p) {
+      const uint4 v = *reinterpret_cast<const uint4*>(codes + rowl * D + p * DP + j);
+      w.x |= v.x << (p * NBITS);
+      w.y |= v.y << (p * NBITS);
+      w.z |= v.z << (p * NBITS);
+      w.w |= v.w << (p * NBITS);
+    }
+    // token blocks of one sequence are contiguous in the quantised part: global row = g*32 + token
+    *reinterpret_cast<uint4*>(packed + (g * kChanTok + (rowl % kChanTok)) * DP + j) = w;
   }
 }
 
@@ -779,14 +868,16 @@ namespace {
 template <typename T>
 int launch_keys_channel(const void* x, uint8_t* packed, void* scale, void* zero, int64_t BH, int64_t S,
                         int64_t S_q, int D, int nbits, cudaStream_t stream) {
-  const int64_t blocks = BH * (S_q / tkv::kChanTok);
+  const int64_t n_blocks = BH * (S_q / tkv::kChanTok);
+  const int per_cta = 512 / D;  // token blocks per CTA of 256 threads
+  const int64_t blocks = (n_blocks + per_cta - 1) / per_cta;
   TKV_REQUIRE(blocks <= 0x7fffffffLL, TKV_ERR_INVALID, "quantize_keys_per_channel: tensor too large");
   if (nbits == 4)
-    tkv::quantize_keys_channel_kernel<T, 4><<<(int)blocks, D, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D);
+    tkv::quantize_keys_channel_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D, n_blocks);
   else
-    tkv::quantize_keys_channel_kernel<T, 2><<<(int)blocks, D, 0, stream>>>(
-        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D);
+    tkv::quantize_keys_channel_kernel<T, 2><<<(int)blocks, 256, 0, stream>>>(
+        (const T*)x, packed, (__half*)scale, (__half*)zero, S, S_q, D, n_blocks);
   TKV_CUDA(cudaGetLastError());
   return TKV_OK;
 }
@@ -803,6 +894,11 @@ extern "C" int tkv_quantize_keys_per_channel(const void* x, int in_dtype, uint8_
               "quantize_keys_per_channel: built for power-of-two head_dim in [32, 256], got %d", D);
   if (BH == 0 || S_q == 0) return TKV_OK;
   TKV_REQUIRE(x && packed && scale && zero, TKV_ERR_INVALID, "quantize_keys_per_channel: null pointer");
+  TKV_REQUIRE(D * nbits / 8 >= 16, TKV_ERR_UNSUPPORTED,
+              "quantize_keys_per_channel: packed rows of %d bytes are shorter than 16", D * nbits / 8);
+  TKV_REQUIRE(aligned16(packed) && ((uintptr_t)x & 7u) == 0 && ((uintptr_t)scale & 3u) == 0 &&
+                  ((uintptr_t)zero & 3u) == 0,
+              TKV_ERR_ALIGN, "quantize_keys_per_channel: packed must be 16-byte, x 8-byte, scale and zero 4-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   switch (in_dtype) {
     case TKV_DTYPE_F16: return launch_keys_channel<__half>(x, packed, scale, zero, BH, S, S_q, D, nbits, s);
