@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(256)
     quantize_pack_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed,
                          __half* __restrict__ scale, __half* __restrict__ zero, int64_t rows,
                          int tpr_shift, int lpg_shift, const AppendMap am) {
-  constexpr int P = 8 / NBITS, LOG2P = NBITS == 4 ? 1 : 2;
+  constexpr int LOG2P = NBITS == 4 ? 1 : 2;  // P = 8 / NBITS codes per packed byte
   constexpr float QMAX = float((1 << NBITS) - 1);
   constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: x + kMagic holds rint(x) in its low mantissa bits
   constexpr bool k16 = !std::is_same<T, float>::value;
