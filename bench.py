@@ -702,8 +702,8 @@ def run_ours(args):
     seq_lens, valid_frac = None, 1.0
     S_loc = ctx
     if name == "ragged-b16":
-        from tritonkv_b200.workloads import ragged_seq_lens
-        lens = ragged_seq_lens(B_loc, 1024, ctx, seed=seed)
+        g = torch.Generator(device="cpu").manual_seed(seed)  # lengths uniform in [1024, ctx]
+        lens = torch.randint(1024, ctx + 1, (B_loc,), generator=g, dtype=torch.int64).to(torch.int32)
         S_loc = int(lens.max())
         seq_lens = lens.to(device)
         valid_frac = float(lens.sum()) / (B_loc * S_loc)

@@ -14,7 +14,7 @@ from oracle import tkv_oracle as O
 from tritonkv_b200 import quantize as Q
 from tritonkv_b200.kernels import (combine_splits, fp16_decode_attention, fused_decode_attention,
                                    triton_available)
-from tritonkv_b200.workloads import make_random_kv, ragged_seq_lens
+from oracle.workloads import make_random_kv, ragged_seq_lens
 
 from util import ATOL, RTOL, assert_close, c_oracle_attention, oracle_attention, to_oracle
 
@@ -428,7 +428,7 @@ def test_ragged_sweep_grid(D, HQ, HKV, nbits, gs):
     """The ragged batched sweep (batch 16, per-sequence lengths from a seed, 1 % of the K
     entries x20) over its whole (D, heads, nbits, group) grid, at lengths the oracle does
     in a second (the full lengths are covered by the property test below)."""
-    from tritonkv_b200.workloads import make_entry_outlier_k
+    from oracle.workloads import make_entry_outlier_k
 
     B, S = 16, 1536
     lens = ragged_seq_lens(B, 48, S, seed=D + HQ + nbits + gs)

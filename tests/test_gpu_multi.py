@@ -25,7 +25,7 @@ def _worker(rank, world, port, ret):
     from tritonkv_b200 import parallel as P
     from tritonkv_b200 import quantize as Q
     from tritonkv_b200.kernels import fused_decode_attention
-    from tritonkv_b200.workloads import make_random_kv
+    from oracle.workloads import make_random_kv
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

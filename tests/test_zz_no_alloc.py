@@ -20,7 +20,7 @@ import torch
 from tritonkv_b200 import _cabi
 from tritonkv_b200 import quantize as Q
 from tritonkv_b200.kernels import fused_decode_attention
-from tritonkv_b200.workloads import make_random_kv
+from oracle.workloads import make_random_kv
 
 from util import assert_close, oracle_attention
 
