@@ -107,3 +107,7 @@ def test_argument_errors():
         kivi_decode_attention(q, bad)
     with pytest.raises(ValueError):
         Q.quantize_keys_per_channel(k[0], 4)               # not (B, HKV, S, D)
+    with pytest.raises(ValueError, match="shorter than 16"):
+        Q.quantize_keys_per_channel(k[..., :32].contiguous(), 2)   # packed rows of 8 bytes
+    kc, _ = Q.quantize_keys_per_channel(k[..., :32].contiguous(), 4)  # 16-byte rows: the smallest
+    assert kc.packed.shape == (1, 2, 64, 16)
