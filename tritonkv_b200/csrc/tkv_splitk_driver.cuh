@@ -38,6 +38,25 @@ namespace tkv {
 constexpr int kMaxRaggedB = 512;  // sequences whose tile prefix fits the kernel's static shared memory
 constexpr float kLazyTau = 4.0f;  // head-room of the lazily raised softmax exponent (log2 units)
 
+// n / d for 0 <= n < 2^31 and a divisor fixed per launch, as a multiply-high, an add and a
+// shift: the pair is made on the host.  (A 32-bit division is ~40 instructions, a 64-bit one
+// several hundred cycles; a segment look-up has five and every warp performs it.)
+struct FastDiv {
+  uint32_t mul, shift;
+};
+inline FastDiv make_fastdiv(int d) {
+  const uint64_t dd = d > 1 ? (uint64_t)d : 1;
+  uint32_t l = 0;
+  while ((1ull << l) < dd) ++l;
+  FastDiv f;
+  f.mul = (uint32_t)(((1ull << 32) * ((1ull << l) - dd)) / dd + 1);
+  f.shift = l;
+  return f;
+}
+__device__ __forceinline__ int fast_div(int n, FastDiv f) {
+  return (int)((__umulhi((uint32_t)n, f.mul) + (uint32_t)n) >> f.shift);
+}
+
 struct SplitSched {
   int persistent;  // 0: CTA c <-> unit c (ragged batches with explicit splits); 1: balanced
                    // tile ranges over the global tile sequence; 2: SEG CTAs per unit, ranges
@@ -53,6 +72,7 @@ struct SplitSched {
   int grid;        // CTAs
   int HKVc;        // HKV * head chunks
   int variant;     // which kernel instantiation the plan was made for (set by the planner)
+  FastDiv dSEG, dNS, dHKVc, dTseq, dTUf, dTC, dHch;  // divisions by SEG, NS, HKVc, T_seq, TUf, TC, head chunks
 };
 
 // `unit_aligned`: whether the plan may be the unit-aligned one (mode 2); a kernel family that
@@ -115,6 +135,13 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
     }
   }
   s.nslots = s.NS * s.SEG;
+  s.dSEG = make_fastdiv(s.SEG);
+  s.dNS = make_fastdiv(s.NS);
+  s.dHKVc = make_fastdiv(s.HKVc);
+  s.dTseq = make_fastdiv(s.T_seq);
+  s.dTUf = make_fastdiv(s.TUf);
+  s.dTC = make_fastdiv(s.TC);
+  s.dHch = make_fastdiv(hchunks);
   return s;
 }
 
@@ -135,16 +162,16 @@ template <int kTok>
 __device__ __forceinline__ Segment segment_at(const DecodeParams& p, const SplitSched& sc, int g,
                                               int g1, int cta) {
   Segment s;
-  const int bh = g / sc.T_seq;
+  const int bh = fast_div(g, sc.dTseq);
   const int r = g - bh * sc.T_seq;
-  const int sp = min(r / sc.TUf, sc.NS - 1);
+  const int sp = min(fast_div(r, sc.dTUf), sc.NS - 1);
   const int tu = r - sp * sc.TUf;
   const int TU = (sp == sc.NS - 1) ? sc.TUl : sc.TUf;
   const int unit_start = bh * sc.T_seq + sp * sc.TUf;
   const int unit_end = unit_start + TU;
-  s.b = bh / sc.HKVc;
+  s.b = fast_div(bh, sc.dHKVc);
   const int hk = bh - s.b * sc.HKVc;
-  s.hkv = hk / p.hchunks;
+  s.hkv = fast_div(hk, sc.dHch);
   s.hc = hk - s.hkv * p.hchunks;
   s.split = sp;
   const int lo_unit = sp * p.split_size;
@@ -152,7 +179,7 @@ __device__ __forceinline__ Segment segment_at(const DecodeParams& p, const Split
   s.lo_tok = lo_unit + tu * kTok;
   s.g_end = min(g1, unit_end);
   s.ntiles = s.g_end - g;
-  const int c_first = unit_start / sc.TC;
+  const int c_first = fast_div(unit_start, sc.dTC);
   const int seg = cta - c_first;
   s.slot = sp * sc.SEG + seg;
   if (s.g_end == unit_end && seg + 1 < sc.SEG) {
@@ -184,7 +211,7 @@ __device__ __forceinline__ Segment ragged_segment_at(const DecodeParams& p, cons
   const int tile = r - hk * t_b;
   const int unit_start = g - tile, unit_end = unit_start + t_b;
   s.b = b;
-  s.hkv = hk / p.hchunks;
+  s.hkv = fast_div(hk, sc.dHch);
   s.hc = hk - s.hkv * p.hchunks;
   s.split = 0;
   s.hi = min(max(p.seq_lens[b], 0), p.S);
@@ -222,6 +249,8 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
                   const SplitSched sc) {
   constexpr int WARPS = Policy::WARPS, STAGES = Policy::STAGES, D = Policy::D;
   constexpr int kTok = Policy::TOK;
+  constexpr int kLog2D = D == 64 ? 6 : (D == 128 ? 7 : (D == 256 ? 8 : 5));
+  static_assert((1 << kLog2D) == D, "head_dim is a power of two between 32 and 256");
   constexpr int STAGE_BYTES = Policy::STAGE_BYTES;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte alignment");
   static_assert(STAGES >= (Policy::PIPELINED ? 3 : 2),
@@ -272,9 +301,9 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   }
   const int q_esz = p.q_dtype == TKV_DTYPE_F32 ? 4 : 2;
   auto prefetch_q = [&](int slot, int b, int hkv, int hc) {
-    const int row_bytes = D * q_esz, cpr = row_bytes >> 4;
+    const int row_bytes = D * q_esz, cpr = row_bytes >> 4, cpr_shift = q_esz == 4 ? kLog2D - 2 : kLog2D - 3;
     for (int i = threadIdx.x; i < kHeadsPerCta * cpr; i += WARPS * 32) {
-      const int h = i / cpr, c = i - h * cpr;
+      const int h = i >> cpr_shift, c = i - (h << cpr_shift);
       const int hg = hc * kHeadsPerCta + h;
       const bool ok = hg < p.group;
       const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
@@ -358,19 +387,21 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
     seg = seg_at(g0, g1);
   } else if (sc.persistent == 2) {  // MODE 2 from here on
     // unit-aligned: CTA j of the unit's SEG takes tiles [j*TU/SEG, (j+1)*TU/SEG) of the unit
-    const int u = cta / sc.SEG, j = cta - u * sc.SEG;
-    const int bh = u / sc.NS;
+    const int u = fast_div(cta, sc.dSEG), j = cta - u * sc.SEG;
+    const int bh = fast_div(u, sc.dNS);
     seg.split = u - bh * sc.NS;
-    seg.b = bh / sc.HKVc;
+    seg.b = fast_div(bh, sc.dHKVc);
     const int hk = bh - seg.b * sc.HKVc;
-    seg.hkv = hk / p.hchunks;
+    seg.hkv = fast_div(hk, sc.dHch);
     seg.hc = hk - seg.hkv * p.hchunks;
     const int TU = (seg.split == sc.NS - 1) ? sc.TUl : sc.TUf;
-    const int t0 = (int)(((int64_t)j * TU) / sc.SEG);
+    // floor(j*TU/SEG) = j*(TU/SEG) + floor(j*(TU%SEG)/SEG): all products stay below SEG^2
+    const int tq = fast_div(TU, sc.dSEG), tr = TU - tq * sc.SEG;
+    const int t0 = j * tq + fast_div(j * tr, sc.dSEG);
     const int lo_unit = seg.split * p.split_size;
     seg.hi = min(lo_unit + p.split_size, p.S);
     seg.lo_tok = lo_unit + t0 * kTok;
-    seg.ntiles = (int)(((int64_t)(j + 1) * TU) / sc.SEG) - t0;
+    seg.ntiles = (j + 1) * tq + fast_div((j + 1) * tr, sc.dSEG) - t0;
     seg.slot = seg.split * sc.SEG + j;
     seg.fill_from = seg.fill_to = -1;
     g0 = 0;
@@ -392,11 +423,11 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   } else {
     // static: CTA <-> unit, per-sequence length from seq_lens
     pdl_wait();
-    const int bh = cta / sc.NS;
+    const int bh = fast_div(cta, sc.dNS);
     seg.split = cta - bh * sc.NS;
-    seg.b = bh / sc.HKVc;
+    seg.b = fast_div(bh, sc.dHKVc);
     const int hk = bh - seg.b * sc.HKVc;
-    seg.hkv = hk / p.hchunks;
+    seg.hkv = fast_div(hk, sc.dHch);
     seg.hc = hk - seg.hkv * p.hchunks;
     const int S_b = p.seq_lens ? min(max(p.seq_lens[seg.b], 0), p.S) : p.S;
     const int lo_unit = seg.split * p.split_size;
