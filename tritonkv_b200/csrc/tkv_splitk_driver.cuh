@@ -53,6 +53,14 @@ inline FastDiv make_fastdiv(int d) {
   f.shift = l;
   return f;
 }
+__device__ __forceinline__ FastDiv make_fastdiv_device(int d) {  // one 64-bit division, once per CTA
+  const uint32_t dd = d > 1 ? (uint32_t)d : 1u;
+  const uint32_t l = dd > 1 ? 32u - (uint32_t)__clz((int)(dd - 1)) : 0u;
+  FastDiv f;
+  f.mul = (uint32_t)(((1ull << 32) * ((1ull << l) - dd)) / dd + 1);
+  f.shift = l;
+  return f;
+}
 __device__ __forceinline__ int fast_div(int n, FastDiv f) {
   return (int)((__umulhi((uint32_t)n, f.mul) + (uint32_t)n) >> f.shift);
 }
@@ -88,7 +96,7 @@ inline SplitSched make_sched(int B, int HKV, int hchunks, int S, int num_splits,
   if (num_splits == 1) s.TUf = s.TUl;
   s.T_seq = (num_splits - 1) * s.TUf + s.TUl;
   const int64_t units = (int64_t)B * s.HKVc * num_splits;
-  if (ragged && num_splits == 1 && B <= kMaxRaggedB) {
+  if (ragged && num_splits == 1 && B <= kMaxRaggedB && (int64_t)B * s.TUf < (1 << 25)) {  // (prefix words hold 25 bits of tiles)
     // Lengths live on the device, so only bounds are known here: one wave of CTAs, and
     // per unit at most min(tiles, wave/HKVc + 2) segments (a unit of t tiles is cut into
     // at most t/TC + 2 ranges and TC >= HKVc * t / wave).
@@ -194,31 +202,37 @@ __device__ __forceinline__ Segment segment_at(const DecodeParams& p, const Split
 
 // Ragged batches: `pref[b]` = tiles of sequences 0..b-1 (one KV head), so unit
 // (b, hk) starts at global tile HKVc*pref[b] + hk*t_b with t_b = pref[b+1] - pref[b].
+// An entry of `pref` is (tiles before the sequence) << kRemBits | (tokens in its last tile - 1),
+// so a sequence's length comes out of the same words as its tile range; `dTC` divides by the
+// tiles per CTA.
+constexpr int kRemBits = 6;  // a tile has at most 64 tokens
 template <int kTok>
 __device__ __forceinline__ Segment ragged_segment_at(const DecodeParams& p, const SplitSched& sc,
-                                                     const int* pref, int TC, int g, int g1,
+                                                     const int* pref, FastDiv dTC, int g, int g1,
                                                      int cta) {
+  static_assert(kTok <= (1 << kRemBits), "the remainder field holds tokens of one tile");
   Segment s;
   int lo = 0, hi = p.B;  // largest b with HKVc*pref[b] <= g (sequences without tiles are skipped)
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
-    if (sc.HKVc * pref[mid] <= g) lo = mid; else hi = mid;
+    if (sc.HKVc * (pref[mid] >> kRemBits) <= g) lo = mid; else hi = mid;
   }
   const int b = lo;
-  const int t_b = pref[b + 1] - pref[b];
-  const int r = g - sc.HKVc * pref[b];
-  const int hk = r / t_b;
+  const int word = pref[b], before = word >> kRemBits;
+  const int t_b = (pref[b + 1] >> kRemBits) - before;
+  const int r = g - sc.HKVc * before;
+  const int hk = (int)((uint32_t)r / (uint32_t)t_b);  // (unsigned: half the instructions of a signed division)
   const int tile = r - hk * t_b;
   const int unit_start = g - tile, unit_end = unit_start + t_b;
   s.b = b;
   s.hkv = fast_div(hk, sc.dHch);
   s.hc = hk - s.hkv * p.hchunks;
   s.split = 0;
-  s.hi = min(max(p.seq_lens[b], 0), p.S);
+  s.hi = (t_b - 1) * kTok + (word & ((1 << kRemBits) - 1)) + 1;  // the length, clamped to [1, S] (t_b >= 1 here)
   s.lo_tok = tile * kTok;
   s.g_end = min(g1, unit_end);
   s.ntiles = s.g_end - g;
-  const int seg = cta - unit_start / TC;
+  const int seg = cta - fast_div(unit_start, dTC);
   s.slot = seg;
   if (s.g_end == unit_end && seg + 1 < sc.SEG) {
     s.fill_from = seg + 1;
@@ -317,11 +331,12 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
   // ---- this CTA's tile range ----
   int g0, g1;
   int TC = sc.TC;  // tiles per CTA (computed here for ragged batches)
+  FastDiv dTC = sc.dTC;
   Segment seg;
   constexpr bool kMulti = (MODE & 1) != 0;  // a CTA may serve several segments
   auto seg_at = [&](int g, int g_hi) {
     if constexpr (MODE == 3) {
-      return ragged_segment_at<kTok>(p, sc, s_pref, TC, g, g_hi, cta);
+      return ragged_segment_at<kTok>(p, sc, s_pref, dTC, g, g_hi, cta);
     } else if constexpr (MODE == 1) {
       return segment_at<kTok>(p, sc, g, g_hi, cta);
     } else {
@@ -350,18 +365,21 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
           const int y = __shfl_up_sync(kFullMask, incl, off);
           if (lane >= off) incl += y;
         }
-        if (b < p.B) s_pref[b] = carry + incl - t;
+        if (b < p.B)
+          s_pref[b] = ((carry + incl - t) << kRemBits) | (t > 0 ? len - (t - 1) * kTok - 1 : 0);
         carry += __shfl_sync(kFullMask, incl, 31);
       }
-      if (lane == 0) s_pref[p.B] = carry;
+      if (lane == 0) s_pref[p.B] = carry << kRemBits;
     }
     __syncthreads();
-    const int T = sc.HKVc * s_pref[p.B];
+    const int T = sc.HKVc * (s_pref[p.B] >> kRemBits);
     TC = max(1, (T + (int)gridDim.x - 1) / (int)gridDim.x);
+    dTC = make_fastdiv_device(TC);
     // units without tokens are touched by no range: their slots are marked empty here
     for (int u = cta; u < p.B * sc.HKVc; u += gridDim.x) {
       const int b = u / sc.HKVc, hk = u - b * sc.HKVc;
-      if (s_pref[b + 1] == s_pref[b] && p.partials) {
+      const bool no_tiles = (s_pref[b + 1] >> kRemBits) == (s_pref[b] >> kRemBits);
+      if (no_tiles && p.partials) {
         const int hkv = hk / p.hchunks, hc = hk - hkv * p.hchunks;
         for (int idx = threadIdx.x; idx < kHeadsPerCta * sc.SEG; idx += WARPS * 32) {
           const int h = idx / sc.SEG, j = idx - h * sc.SEG;
@@ -372,7 +390,7 @@ __global__ void __launch_bounds__(Policy::WARPS * 32, Policy::MIN_CTAS)
             p.l[hq * sc.nslots + j] = 0.f;
           }
         }
-      } else if (s_pref[b + 1] == s_pref[b]) {
+      } else if (no_tiles) {
         for (int idx = threadIdx.x; idx < kHeadsPerCta * D; idx += WARPS * 32) {
           const int h = idx / D, d = idx - h * D;
           const int hkv = hk / p.hchunks, hc = hk - hkv * p.hchunks;
