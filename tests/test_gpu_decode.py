@@ -193,6 +193,28 @@ def test_query_dtypes(q_dtype):
     assert_close(got, oracle_attention(qq.to(torch.float16), kq, vq), str(q_dtype))
 
 
+@pytest.mark.parametrize("nbits", [4, 2])
+@pytest.mark.parametrize("k_first", [True, False])
+@pytest.mark.parametrize("B,S", [(1, 4096), (16, 2048)])
+def test_code_tensors_in_either_address_order(nbits, k_first, B, S):
+    """The K and the V code tensor are fetched through ONE tensor map that spans both (the lower
+    address first); whichever of the two lies higher, the result is the same bits."""
+    HQ, HKV, D = 32, 8, 128
+    q, k, v = make_random_kv(B, HQ, HKV, S, D, device=DEV, seed=91)
+    kq, vq = Q.quantize_kv(k, v, nbits, 32)
+    ref = fused_decode_attention(q, kq, vq)
+    n = kq.packed.numel()
+    buf = torch.empty(2 * n + 4096, dtype=torch.uint8, device=DEV)
+    lo, hi = buf[:n].view(kq.packed.shape), buf[n + 4096:].view(kq.packed.shape)
+    kp, vp = (lo, hi) if k_first else (hi, lo)
+    kp.copy_(kq.packed)
+    vp.copy_(vq.packed)
+    assert (kp.data_ptr() < vp.data_ptr()) == k_first
+    k2 = Q.QuantizedTensor(kp, kq.scale, kq.zero, nbits, 32, D)
+    v2 = Q.QuantizedTensor(vp, vq.scale, vq.zero, nbits, 32, D)
+    assert torch.equal(fused_decode_attention(q, k2, v2), ref)
+
+
 def test_sm_scale_out_and_workspace_reuse():
     q, k, v = make_random_kv(2, 8, 2, 2048, 128, device=DEV, seed=41)
     kq, vq = Q.quantize_kv(k, v, 4, 32)

@@ -258,6 +258,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
+// 3-D tiled TMA load (c0 innermost, a multiple of 16 bytes).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tensor_map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(dst),
+      "l"(tensor_map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 // Warm the descriptor cache for a tensor map that lives in kernel-parameter space.
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -144,7 +144,7 @@ struct FusedPolicy {
   static constexpr int NACC = C::NACC, ACC_DIMS = C::ACC_DIMS;
 
   struct Maps {
-    CUtensorMap k, v;
+    CUtensorMap k, v;  // with kv_one: `k` spans both tensors and `v` is unused
   };
   struct Query {
     uint32_t qf[NCH][2];  // B operand of the score MMA; bit slice p is pre-scaled by 2^(-NBITS p)
@@ -155,6 +155,7 @@ struct FusedPolicy {
     uint32_t o_kz;    // byte offset of this lane's K zero-point word (token g)
     uint32_t o_vz;    // byte offset of this lane's first V zero-point (token 2t, group g mod NG)
     uint32_t ones;    // (1, 1) in f16 on lanes 0-3: row 8 of the zero-point MMA sums the p's
+    uint32_t kofs, vofs;  // where the K and the V tile sit inside a stage
   };
   struct Accum {
     float m_ref0, m_ref1;    // exponent the probabilities refer to (same on the 8 lanes of a head)
@@ -197,8 +198,12 @@ struct FusedPolicy {
       // wide view: the tensor is [bytes/128, 128]; narrow view: [tokens, DP]
       constexpr int SH = (DP == 64) ? 1 : (DP == 32) ? 2 : 3;  // row*DP/128 = row >> SH
       const int c1 = p.wide ? (row >> SH) : row;
-      tma_load_2d(st, &maps.k, 0, c1, bar);
-      tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
+      if (p.kv_one) {
+        tma_load_3d(st, &maps.k, 0, c1, 0, bar);
+      } else {
+        tma_load_2d(st, &maps.k, 0, c1, bar);
+        tma_load_2d(st + C::CODE_BYTES, &maps.v, 0, c1, bar);
+      }
     }
     // Scale/zero: 16-byte cp.async per lane (a bulk-copy instruction costs the issuing warp
     // ~100+ cycles each, four of them per tile were a third of the loop time); every lane
@@ -296,6 +301,8 @@ struct FusedPolicy {
     qq.o_kz = (NG >= 2) ? (g * NG + ((2 * t) % NG)) * 2 : g * 2;
     qq.o_vz = ((2 * t) * NG + (g % NG)) * 2;
     qq.ones = (lane < 4) ? 0x3C003C00u : 0u;
+    qq.kofs = (p.kv_one && p.k_second) ? C::CODE_BYTES : 0;
+    qq.vofs = C::CODE_BYTES - qq.kofs;
   }
 
   // Query fragments of a segment are the same for the four warps: each warp builds the
@@ -412,7 +419,7 @@ struct FusedPolicy {
   __device__ static __forceinline__ void scores_kchan(Scores& out, const Query& qq, uint32_t st,
                                                       int left, float qk_scale, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t kc = st;
+    const uint32_t kc = st + qq.kofs;
     const uint32_t ms = st + 2 * C::CODE_BYTES;
     const uint32_t ks_r = ms + t * 8;                     // dims 16ch + 4t .. 16ch + 4t + 3 of a chunk
     const uint32_t kz_r = ms + C::META_STRIDE + t * 8;
@@ -497,7 +504,7 @@ struct FusedPolicy {
       return;
     }
     const int g = lane >> 2;
-    const uint32_t kc = st;
+    const uint32_t kc = st + qq.kofs;
     uint32_t ms = st + 2 * C::CODE_BYTES;
     if constexpr (NG == 1) ms += lds_u32(ms + C::SHIFT_WORD);  // 0 or 2, see FusedCfg::META_STRIDE
     const uint32_t ks_a = ms + qq.o_row;
@@ -596,7 +603,7 @@ struct FusedPolicy {
   // Online softmax update and O^T += V^T P^T for the tile whose scores are `in`.
   __device__ static __forceinline__ void update(Accum& ac, const Query& qq, Scores& in,
                                                 uint32_t st, uint8_t*, int left, int lane) {
-    const uint32_t vc = st + C::CODE_BYTES;
+    const uint32_t vc = st + qq.vofs;
     uint32_t ms = st + 2 * C::CODE_BYTES;
     if constexpr (NG == 1) ms += lds_u32(ms + C::SHIFT_WORD);
     const uint32_t vs_a = ms + 2 * C::META_STRIDE + qq.o_row;
@@ -825,7 +832,12 @@ static int fused_launch_one(const DecodeParams& p, const SplitSched& sc, cudaStr
   typename P::Maps maps;
   const int64_t rows = (int64_t)p.B * p.HKV * p.S;
   int rc;
-  if (p.wide) {
+  if (p.kv_one) {
+    const uint8_t* lo = p.k_second ? p.vp : p.kp;
+    const uint8_t* hi = p.k_second ? p.kp : p.vp;
+    rc = make_pair_map(&maps.k, lo, (uint64_t)(hi - lo), rows * C::DP / 128, C::kTok * C::DP / 128);
+    maps.v = maps.k;
+  } else if (p.wide) {
     // [bytes/128, 128] view, box = a tile's bytes as 128-byte rows, 128B swizzle
     rc = make_row_map(&maps.k, p.kp, rows * C::DP / 128, 128, 128, C::kTok * C::DP / 128);
     if (rc != TKV_OK) return rc;
@@ -944,6 +956,17 @@ extern "C" int tkv_fused_decode(const void* q, int q_dtype, const uint8_t* k_pac
   }
   // 128-byte-row view of the code tensors: every sequence must start on a 128-byte boundary
   p.wide = (((int64_t)S * D * nbits / 8) % 128 == 0) ? 1 : 0;
+  {
+    // one tensor map over both code tensors when a tile fills whole 1024-byte swizzle atoms
+    const uint8_t* lo = k_packed < v_packed ? k_packed : v_packed;
+    const uint8_t* hi = k_packed < v_packed ? v_packed : k_packed;
+    const uint64_t gap = (uint64_t)(hi - lo);
+    const int64_t tensor_bytes = (int64_t)B * HKV * S * (D * nbits / 8);
+    const bool ok = p.wide && ((32 * (D * nbits / 8)) % 1024 == 0) && gap % 16 == 0 && gap < (1ull << 40) &&
+                    gap >= (uint64_t)tensor_bytes;
+    p.kv_one = ok ? 1 : 0;
+    p.k_second = (ok && k_packed > v_packed) ? 1 : 0;
+  }
   const bool kchan = (flags & TKV_FLAG_K_PER_CHANNEL) != 0;
   if (kchan) {
     // k_scale / k_zero are (B, HKV, S/32, D): one row per block of 32 tokens, so every tile

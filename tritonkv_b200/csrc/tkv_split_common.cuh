@@ -36,6 +36,8 @@ struct DecodeParams {
   int meta_aligned;  // bytes every scale/zero tile start is aligned to: 16, 8, 4, or 0 (2 bytes only)
   int meta_phase;    // with meta_aligned == 0: the scale/zero pointers modulo 4 (0 or 2)
   int wide;          // 1: code tensors are fetched as 128-byte rows (128B TMA swizzle)
+  int kv_one;        // 1: one 3-D tensor map spans the K and the V code tensor (one TMA per tile)
+  int k_second;      // with kv_one: the K tensor lies above V, its tile lands second in the stage
 };
 
 // Running softmax state of one warp for the two heads (2t, 2t+1) a lane owns.

@@ -790,6 +790,47 @@ inline int make_row_map(CUtensorMap* tm, const void* base, int64_t rows, int row
   return TKV_OK;
 }
 
+// One map over two byte matrices [rows, 128] that lie `gap` bytes apart (the lower one first):
+// dims {128, rows, 2}, box {128, box_rows, 2}, 128-byte swizzle.
+inline int make_pair_map(CUtensorMap* tm, const void* lower, uint64_t gap, int64_t rows, int box_rows) {
+  // A decode loop encodes the same map every step: keep the last ones per thread.
+  struct Entry {
+    const void* lower;
+    uint64_t gap;
+    int64_t rows;
+    int box_rows;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 4;
+  thread_local Entry cache[kEntries] = {};
+  thread_local int next = 0;
+  for (int i = 0; i < kEntries; ++i) {
+    const Entry& e = cache[i];
+    if (e.lower == lower && e.gap == gap && e.rows == rows && e.box_rows == box_rows && e.lower != nullptr) {
+      *tm = e.map;
+      return TKV_OK;
+    }
+  }
+  EncodeTiledFn fn = encode_tiled_fn();
+  TKV_REQUIRE(fn != nullptr, TKV_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  const cuuint64_t gdim[3] = {128, (cuuint64_t)rows, 2};
+  const cuuint64_t gstride[2] = {128, (cuuint64_t)gap};
+  const cuuint32_t box[3] = {128, (cuuint32_t)box_rows, 2};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(lower), gdim, gstride, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TKV_REQUIRE(r == CUDA_SUCCESS, TKV_ERR_CUDA, "cuTensorMapEncodeTiled (pair) failed with CUresult %d", (int)r);
+  Entry& e = cache[next];
+  next = (next + 1) % kEntries;
+  e.lower = lower;
+  e.gap = gap;
+  e.rows = rows;
+  e.box_rows = box_rows;
+  e.map = *tm;
+  return TKV_OK;
+}
+
 // MODES: bit m set = schedule mode m (1, 2, 3) is built for this policy.
 template <class Policy, int MODES = 0xE>
 struct SplitLaunch {
