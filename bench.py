@@ -62,10 +62,10 @@ WORKLOADS = {
 # cache bytes of that launch).  Traffic grows in proportion to the cache (every byte is read
 # once, L2 hit rate 1-2 %), so the ratio measured at the capture size carries to the bench size.
 NCU_TRAFFIC_RATIO = {
-    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.08 MB read + 2.39 MB written) / 83.89 MB
-    ("llama8b-b64", 4): (84_079_616 + 2_394_368) / 83_886_080,
-    # profiles/splitk_fused_2bit_llama8b_batch16.md: (50.52 MB read + 7.42 MB written) / 50.33 MB
-    ("llama8b-b64", 2): (50_523_392 + 7_424_000) / 50_331_648,
+    # profiles/splitk_fused_4bit_llama8b_batch16.md: (84.07 MB read + 2.57 MB written) / 83.89 MB
+    ("llama8b-b64", 4): (84_073_216 + 2_570_752) / 83_886_080,
+    # profiles/splitk_fused_2bit_llama8b_batch16.md: (50.51 MB read + 2.05 MB written) / 50.33 MB
+    ("llama8b-b64", 2): (50_514_688 + 2_048_000) / 50_331_648,
     # profiles/splitk_fused_4bit_qwen_ctx65536.md: 21.02 MB read / 20.97 MB
     ("qwen-b1", 4): 21_023_488 / 20_971_520,
 }
