@@ -759,14 +759,8 @@ struct FusedPolicy {
 //    third fewer query loads and epilogues, which is what a step of 2-3 tiles per warp is
 //    made of (measured: batch 1, ctx 65536, 4-bit step 12.4 -> 10.8 us).
 constexpr int kVariantBatched = 0, kVariantLong = 1;
-// (2-bit rows of 128 dims: a 64-token tile is the bytes of a 4-bit 32-token one, so the batched
-// family takes 64 tokens per stage, two stages per warp, one tile at a time -- the per-tile
-// copy issue, barrier wait and bookkeeping serve twice the tokens in the same shared memory;
-// measured 55.3 -> 54.4 us at batch 64.)
 template <int NB, int DD, int GG, bool A16, bool KCHAN = false>
-using BatchedPolicy =
-    std::conditional_t<(NB == 2 && DD == 128 && !KCHAN), FusedPolicy<NB, DD, GG, A16, 64, 4, 2, 3, false, KCHAN>,
-                       FusedPolicy<NB, DD, GG, A16, 32, 4, 3, 3, true, KCHAN>>;
+using BatchedPolicy = FusedPolicy<NB, DD, GG, A16, 32, 4, 3, 3, true, KCHAN>;
 template <int NB, int DD, int GG, bool A16, bool KCHAN = false>
 using LongPolicy = FusedPolicy<NB, DD, GG, A16, 32, 8, 2, 2, false, KCHAN>;
 
