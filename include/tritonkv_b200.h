@@ -191,14 +191,14 @@ int tkv_quantize_keys_per_channel(const void* x, int in_dtype, uint8_t* packed, 
 /* Cross-GPU exchange for a history split over the GPUs of one node (no reference
  * counterpart: the reference is single-GPU).  Each rank owns a receive buffer of
  * 2 * world blocks of `wire_floats` 8-byte pairs {value, step} in the layout
- * [acc rows*D | m rows | l rows], and two 32-bit state words {step, tickets} in its own
- * memory, all zeroed before the first call; the receive buffers are mapped on every rank
+ * [acc rows*D | m rows | l rows], and rows * D/32 32-bit step counters (one per row and 32-dim
+ * slice: `state`) in its own memory, all zeroed before the first call; the receive buffers are mapped on every rank
  * (peer or symmetric memory) and passed as a table of `world` pointers, entry j = rank j's.
  * tkv_combine_push merges this rank's split partials (arguments as tkv_combine_strided,
  * result left unnormalised) and stores them, tagged with the step number, into block
  * (step parity, rank) of every rank's buffer.  tkv_merge_wait, enqueued after it on the
  * same stream, reads the world blocks of this step -- polling each pair until it carries
- * the step -- merges them into out (rows, D) and bumps the step.  The wait is bounded
+ * the step -- merges them into out (rows, D) and bumps the step counters.  The wait is bounded
  * (2^18 polls, a few tenths of a second); on expiry the kernel records bit 1 of tkv_device_status and merges what
  * it has.  Ranks must call the pair in lockstep, one pair per decode step. */
 int tkv_combine_push(const float* acc, const float* m, const float* l, int64_t rows, int NS, int D,
@@ -212,7 +212,7 @@ int tkv_merge_wait(float* out, int64_t rows, int D, void* const* peer_data, void
  * merges this rank's partials of a (row, 32-dim slice) stores the result to every rank and
  * then waits -- with the same bounded wait -- for the same slice of every rank, merges and
  * writes out (rows, D).  One kernel boundary less on the latency chain of a history-split
- * step; same buffers, state words and lockstep rule as the pair above, with which it must
+ * step; same buffers, step counters and lockstep rule as the pair above, with which it must
  * not be mixed within one step. */
 int tkv_combine_exchange(const float* acc, const float* m, const float* l, float* out, int64_t rows,
                          int NS, int D, int64_t acc_row_stride, int64_t acc_slot_stride,

@@ -112,5 +112,6 @@ def test_peer_exchange_layout():
     wire = P.wire_floats(1, 64, 128)
     state_off, total = P.exchange_layout(8, wire)
     assert state_off == 2 * 8 * wire * 8          # two parities x world blocks of 8-byte pairs
-    assert total == state_off + 16 and total % 16 == 0 and state_off % 16 == 0
+    assert total >= state_off + 4 * (wire // 130) * (128 // 32)  # a step counter per (row, 32-dim slice)
+    assert total % 16 == 0 and state_off % 16 == 0
     assert wire % 4 == 0 and wire >= 64 * (128 + 2)

@@ -180,13 +180,13 @@ __global__ void __launch_bounds__(kCombineThreads)
 // and stores the result into block (step parity, own rank) of EVERY rank's buffer.
 // wait-merge reads the world blocks of this step, each thread polling its own pairs until
 // they carry the step (bounded; on expiry it records a status and goes on), merges them,
-// and the last CTA to finish (a ticket counter on local memory) bumps the step.  Two
+// and every CTA bumps the step counter of its (row, slice) in local memory.  Two
 // parities suffice: a rank can only be one step ahead of the slowest, because each step
 // consumes every rank's block.
 constexpr int kMaxPeers = 8;
 struct Exchange {
   uint2* data[kMaxPeers];  // rank j's receive buffer, as mapped in this process
-  uint32_t* state;         // this rank's {step, tickets}, local memory
+  uint32_t* state;         // this rank's step counters, one per (row, 32-dim slice), local memory
   int world, rank, rows, wire;  // wire = pairs per block
 };
 
@@ -257,17 +257,10 @@ __device__ __forceinline__ void wait_merge_store(float* __restrict__ out, int D,
     }
     out[(int64_t)row * D + d0 + tid] = L > 0.f ? a / L : 0.f;
   }
-  // the last CTA to get here bumps the step (local memory only; nothing waits on it
-  // inside this grid, and the next exchange follows this grid in the stream)
-  if (tid == 0) {
-    const uint32_t total = gridDim.x * gridDim.y;
-    const uint32_t ticket = atomicAdd(ex.state + 1, 1u);
-    if (ticket == total - 1) {
-      ex.state[1] = 0;
-      __threadfence();
-      ex.state[0] = step;
-    }
-  }
+  // this CTA's step counter (local memory; only the CTA of the same (row, slice) of the next
+  // exchange reads it, and that grid follows this one in the stream): a plain store, so the
+  // kernel does not end on the round trip of an atomic ticket
+  if (tid == 0) ex.state[blockIdx.x * gridDim.y + blockIdx.y] = step;
 }
 
 // Stores the merged (row, slice) of this rank, tagged with the step, into block
@@ -301,7 +294,8 @@ __global__ void __launch_bounds__(kCombineThreads)
   pdl_launch_dependents();
   pdl_wait();
   const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
-  const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the wait-merge kernel only
+  // the counter of this (row, slice), bumped by the wait-merge kernel only
+  const uint32_t step = ld_volatile_u32(ex.state + blockIdx.x * gridDim.y + blockIdx.y) + 1;
   push_to_peers(c, ex, step, D, row, d0, blockIdx.y == 0);
 }
 
@@ -309,8 +303,8 @@ __global__ void __launch_bounds__(kCombineThreads)
 __global__ void __launch_bounds__(kCombineThreads)
     merge_wait_kernel(float* __restrict__ out, int D, const Exchange ex) {
   pdl_launch_dependents();
-  pdl_wait();  // orders this kernel after the previous wait-merge (the step counter) and the push
-  const uint32_t step = ld_volatile_u32(ex.state) + 1;
+  pdl_wait();  // orders this kernel after the previous wait-merge (the step counters) and the push
+  const uint32_t step = ld_volatile_u32(ex.state + blockIdx.x * gridDim.y + blockIdx.y) + 1;
   wait_merge_store(out, D, ex, step, blockIdx.x, blockIdx.y * kCombineSlice);
 }
 
@@ -328,7 +322,8 @@ __global__ void __launch_bounds__(kCombineThreads)
   const int d0 = blockIdx.y * kCombineSlice;
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t step = ld_volatile_u32(ex.state) + 1;  // bumped by the last CTA of the previous exchange
+  // bumped by the same CTA of the previous exchange
+  const uint32_t step = ld_volatile_u32(ex.state + blockIdx.x * gridDim.y + blockIdx.y) + 1;
   const CombineResult c = combine_reduce(acc, m, l, NS, a_row, a_slot, ml_row, ml_slot, row, d0);
   push_to_peers(c, ex, step, D, row, d0, blockIdx.y == 0);
   wait_merge_store(out, D, ex, step, row, d0);

@@ -108,10 +108,11 @@ def merge_gathered(gathered: torch.Tensor, B: int, HQ: int, D: int,
 
 
 def exchange_layout(world: int, wire: int) -> tuple[int, int]:
-    """Byte offset of the state words and total bytes of one rank's symmetric buffer:
-    ``2 * world`` blocks of ``wire`` 8-byte pairs {value, step} | {step, tickets}."""
+    """Byte offset of the step counters and total bytes of one rank's symmetric buffer:
+    ``2 * world`` blocks of ``wire`` 8-byte pairs {value, step}, then one 32-bit step counter per
+    (row, 32-dim slice) of the output -- ``wire // 32`` words hold them (wire = rows * (D + 2))."""
     state_off = 2 * world * wire * 8
-    return state_off, state_off + 16
+    return state_off, state_off + (4 * (wire // 32) + 15) // 16 * 16
 
 
 class PeerExchange:
