@@ -27,6 +27,26 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def all_f16_patterns(order: str, seed: int = 5) -> np.ndarray:
+    """All 65536 fp16 bit patterns as a (1, 2, 256, 128) tensor: ``sorted`` (finite values in
+    ascending order, then the non-finite ones: a group holds neighbouring values),
+    ``shuffled``, or ``finite_shuffled`` (non-finite patterns replaced by repeats).  -0 is
+    replaced by +0: which zero a minimum over {-0, +0} returns is not something to pin."""
+    bits = np.arange(65536, dtype=np.uint16)
+    bits[0x8000] = 0
+    vals = bits.view(np.float16)
+    if order == "sorted":
+        finite = vals[np.isfinite(vals)]
+        finite = finite[np.argsort(finite.astype(np.float32), kind="stable")]
+        vals = np.concatenate([finite, vals[~np.isfinite(vals)]])
+    else:
+        if order == "finite_shuffled":
+            vals = vals[np.isfinite(vals)]
+            vals = np.concatenate([vals, vals[: 65536 - len(vals)]])
+        vals = np.random.default_rng(seed).permutation(vals)
+    return np.ascontiguousarray(vals.reshape(1, 2, 256, 128))
+
+
 def main(ref_root: str) -> None:
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_root)
@@ -112,6 +132,23 @@ def main(ref_root: str) -> None:
             out[f"scale_{key}"] = qt.scale.numpy()
             out[f"zero_{key}"] = qt.zero.numpy()
     np.savez_compressed(os.path.join(HERE, "quantize_edges.npz"), **out)
+
+    # ---- 2c. every fp16 bit pattern through the reference's quantiser ------
+    # (what the CUDA quantiser's reciprocal-with-redo arithmetic has to reproduce bit for bit:
+    # exact ties, ranges that underflow fp16, infinities and NaNs in every position)
+    out = {}
+    for order in ("sorted", "shuffled", "finite_shuffled"):
+        x16 = all_f16_patterns(order)
+        out[f"x_{order}"] = x16.view(np.uint16)
+        xt = torch.from_numpy(x16)
+        for nbits in (2, 4):
+            for gs in (8, 32):
+                qt = rq.quantize_groupwise(xt, nbits, gs)
+                key = f"{order}_n{nbits}_g{gs}"
+                out[f"packed_{key}"] = qt.packed.numpy()
+                out[f"scale_{key}"] = qt.scale.numpy().view(np.uint16)
+                out[f"zero_{key}"] = qt.zero.numpy().view(np.uint16)
+    np.savez_compressed(os.path.join(HERE, "quantize_allbits.npz"), **out)
 
     # ---- 3. attention ground truth ----------------------------------------
     out = {}

@@ -172,3 +172,19 @@ def test_split_geometry_matches_reference_launcher():
     assert O.split_geometry(17, 64, 64) == (32, 1, 32)
     assert O.pick_num_splits(1, 2, 128, 592) == 128
     assert O.pick_num_splits(64, 8, 64, 592) == 1
+
+
+@pytest.mark.parametrize("order", ["sorted", "shuffled", "finite_shuffled"])
+@pytest.mark.parametrize("nbits", [2, 4])
+@pytest.mark.parametrize("gs", [8, 32])
+def test_quantize_every_f16_bit_pattern_pinned_on_the_reference(golden_dir, order, nbits, gs):
+    """All 65536 fp16 bit patterns (exact ties, fp16-underflowing ranges, infinities and NaNs in
+    every position) through the oracle's quantiser against what the reference's own
+    ``quantize_groupwise`` returned for them."""
+    g = np.load(os.path.join(golden_dir, "quantize_allbits.npz"))
+    x = g[f"x_{order}"].view(np.float16)
+    ref = O.quantize_groupwise(x, nbits, gs)
+    key = f"{order}_n{nbits}_g{gs}"
+    assert np.array_equal(ref.packed, g[f"packed_{key}"])
+    assert f16_equal(ref.scale, g[f"scale_{key}"].view(np.float16))
+    assert f16_equal(ref.zero, g[f"zero_{key}"].view(np.float16))
