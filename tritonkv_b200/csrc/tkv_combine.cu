@@ -10,7 +10,7 @@
 // shuffles and shared memory.  Splits with m = -inf (empty) weigh zero.
 // With out_m/out_l given, the merged partial is written unnormalised together with
 // (M, L): the wire format of a cross-GPU history split.
-#include "tkv_common.cuh"
+#include "tkv_split_common.cuh"
 
 namespace tkv {
 
@@ -346,7 +346,7 @@ int exchange_device_status(int* status) {
 // lane a float4 slice of D, the slots walked in order.  8192 tiny CTAs of the kernel
 // above would cost more in scheduling than the merge itself.
 constexpr int kSmallWarps = 8;
-constexpr int kSmallMaxNS = 16;
+constexpr int kSmallMaxNS = kSmallCombineMaxSlots;
 
 template <int kMaxNS>  // compile-time bound on the slots, so no load is issued for nothing
 __global__ void __launch_bounds__(kSmallWarps * 32)
@@ -357,7 +357,6 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kSmallWarps + warp;
   if (row >= rows) return;
-  pdl_launch_dependents();  // the next kernel of the stream may start its prologue
   pdl_wait();  // partials come from the kernel launched just before this one
   const float* mrow = m + (int64_t)row * ml_row;
   const float* lrow = l + (int64_t)row * ml_row;
@@ -409,6 +408,9 @@ __global__ void __launch_bounds__(kSmallWarps * 32)
     out_m[row] = M;
     out_l[row] = L;
   }
+  // The kernel behind this one is the next step's balanced split kernel, whose CTAs must all
+  // be resident at once: it may be scheduled only now, when this warp's slot is about to free.
+  pdl_launch_dependents();
 }
 
 }  // namespace tkv
@@ -427,7 +429,7 @@ extern "C" int tkv_combine_strided(const float* acc, const float* m, const float
   TKV_REQUIRE(aligned16(acc) && aligned16(out) && acc_row_stride % 4 == 0 && acc_slot_stride % 4 == 0,
               TKV_ERR_ALIGN, "combine: acc and out must be 16-byte aligned, acc strides multiples of 4");
   TKV_REQUIRE(rows <= 0x7fffffffLL, TKV_ERR_INVALID, "combine: too many rows");
-  if (NS <= kSmallMaxNS && rows >= 256) {
+  if (NS <= kSmallMaxNS && rows >= kSmallCombineMinRows) {
     const unsigned blocks = (unsigned)((rows + kSmallWarps - 1) / kSmallWarps);
 #define TKV_SMALL(N)                                                                          \
   TKV_CUDA(launch_pdl(tkv::combine_small_kernel<N>, dim3(blocks), dim3(kSmallWarps * 32), 0,   \

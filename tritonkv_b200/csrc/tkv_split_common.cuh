@@ -41,6 +41,12 @@ struct DecodeParams {
 };
 
 // Running softmax state of one warp for the two heads (2t, 2t+1) a lane owns.
+// When the warp-per-row combine kernel follows a split kernel (few partial slots, many rows):
+// it lets its programmatic dependents go only at its end, which is what the balanced split
+// kernel of the next step needs (see SplitLaunch::launch).
+constexpr int kSmallCombineMaxSlots = 16;
+constexpr int kSmallCombineMinRows = 256;
+
 struct SoftmaxState {
   float m0, m1;  // running maxima (exp2 domain), identical across the 8 lanes sharing t
   float l0, l1;  // per-lane partial sums of p

@@ -899,18 +899,25 @@ struct SplitLaunch {
                     cudaStream_t stream) {
     int rc = prepare();
     if (rc != TKV_OK) return rc;
-    // Unit-aligned plans (small batches, CTAs of a few microseconds) are launched as
-    // programmatic dependents: the prologue overlaps the tail of the previous kernel of the
-    // stream and the kernel waits for that kernel's completion before its first global
-    // access.  The balanced global plan is launched plainly: its CTAs run for tens of
-    // microseconds and all of them must be resident together, and measured under graph
-    // replay a dependent launch placed one CTA per still-resident combine CTA late (by
-    // 10-30 us at batch 16-32), which the static tile ranges cannot absorb.
+    // The kernel is launched as a programmatic dependent: its prologue overlaps the tail of the
+    // previous kernel of the stream and it waits for that kernel's completion before its first
+    // global access.  For unit-aligned plans (small batches, CTAs of a few microseconds) the
+    // preceding combine kernel lets its dependents go at its start.  The balanced global plan
+    // has CTAs that run for tens of microseconds and must all be resident together: a CTA that
+    // found its place taken by a still-resident combine CTA started 10-30 us late (measured),
+    // which the static tile ranges cannot absorb -- so the combine kernel used behind that
+    // plan (the warp-per-row one) lets its dependents go only when its own work is done, and
+    // what overlaps is the launch itself (batch 8: 17.6 -> 16.8 us per step, batch 64: -0.3 %).
     const dim3 grid(sc.grid), block(Policy::WARPS * 32);
     if (sc.persistent == 1) {
       if constexpr (kHas1) {
-        splitk_kernel<Policy, 1><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
-        TKV_CUDA(cudaGetLastError());
+        // (dependent only where the combine behind the previous step is the one that waits)
+        if (sc.nslots > 1 && sc.nslots <= kSmallCombineMaxSlots && (int64_t)p.B * p.HQ >= kSmallCombineMinRows) {
+          TKV_CUDA(launch_pdl(splitk_kernel<Policy, 1>, grid, block, (size_t)smem_bytes(), stream, maps, p, sc));
+        } else {
+          splitk_kernel<Policy, 1><<<grid, block, smem_bytes(), stream>>>(maps, p, sc);
+          TKV_CUDA(cudaGetLastError());
+        }
         return TKV_OK;
       }
     } else if (sc.persistent == 3) {
